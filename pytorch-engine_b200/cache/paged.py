@@ -7,7 +7,7 @@
   (``max_tokens / 64``), so any mix of sequence lengths whose page-rounded sum fits can be live.
 * Cache entries (one per block that keeps something) with equal needs form a *group* with storage,
   page pool and page table of its own: ``[entries, 2, pages, kv_heads, 64, head_dim]`` for keys and
-  values.  A group with a window gives pages back as soon as every position in them has left the
+  values (two tensors of that layout without the ``2`` when values have a size of their own).  A group with a window gives pages back as soon as every position in them has left the
   window.  A "state" group holds tensors of fixed shape per slot, zeroed when the slot is taken.
 
 The reference keeps one growing buffer per layer for a single sequence
@@ -42,11 +42,13 @@ class CacheView:
 
     @property
     def k_pages(self) -> torch.Tensor:
-        return self.group.storage[self.index, 0]
+        g = self.group
+        return g.storage[self.index, 0] if g.v_storage is None else g.storage[self.index]
 
     @property
     def v_pages(self) -> torch.Tensor:
-        return self.group.storage[self.index, 1]
+        g = self.group
+        return g.storage[self.index, 1] if g.v_storage is None else g.v_storage[self.index]
 
     @property
     def page_table(self) -> torch.Tensor:
@@ -68,6 +70,7 @@ class CacheGroup:
     num_pages: int = 0
     pool: Optional[NumberPool] = None
     storage: Optional[torch.Tensor] = None
+    v_storage: Optional[torch.Tensor] = None   # values of their own size: then ``storage`` holds the keys only
     page_table: Optional[torch.Tensor] = None
     pages_of_slot: Dict[int, List[int]] = field(default_factory=dict)  # logical page -> physical (-1: released)
     state_tensors: Dict[str, torch.Tensor] = field(default_factory=dict)
@@ -117,8 +120,15 @@ class PagedCache:
             g.num_pages = pages_for(self.max_tokens)
             g.pool = NumberPool(g.num_pages, "page")
             # zeros, not uninitialised memory: rows that were never written must hold finite values
-            g.storage = torch.zeros((len(g.entries), 2, g.num_pages, r.kv_heads, PAGE_TOKENS, r.head_dim),
-                                    dtype=self.dtype, device=self.device)
+            if r.value_dim == r.head_dim:
+                g.storage = torch.zeros((len(g.entries), 2, g.num_pages, r.kv_heads, PAGE_TOKENS, r.head_dim),
+                                        dtype=self.dtype, device=self.device)
+            else:
+                # values of another size than keys: two pools of pages with the same numbering
+                g.storage = torch.zeros((len(g.entries), g.num_pages, r.kv_heads, PAGE_TOKENS, r.head_dim),
+                                        dtype=self.dtype, device=self.device)
+                g.v_storage = torch.zeros((len(g.entries), g.num_pages, r.kv_heads, PAGE_TOKENS, r.value_dim),
+                                          dtype=self.dtype, device=self.device)
             g.page_table = torch.full((self.max_slots, self.table_width), -1, dtype=torch.int32, device=self.device)
         elif r.kind == "state":
             for name, shape, dtype_name in r.state_shapes:
@@ -137,8 +147,9 @@ class PagedCache:
     def nbytes(self) -> int:
         total = 0
         for g in self.groups:
-            if g.storage is not None:
-                total += g.storage.numel() * g.storage.element_size()
+            for t in (g.storage, g.v_storage):
+                if t is not None:
+                    total += t.numel() * t.element_size()
             if g.page_table is not None:
                 total += g.page_table.numel() * 4
             for t in g.state_tensors.values():

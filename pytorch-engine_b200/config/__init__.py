@@ -4,9 +4,10 @@ from .registry import (Architecture, architecture, architecture_names, architect
                        preset_names, register_architecture, register_preset_folder, unregister_architecture,
                        unregister_preset_folder)
 from .qwen3 import Qwen3Config
+from .vabelorn import VabelornConfig
 
 __all__ = [
     "ConfigError", "ModelConfig", "read_config_dict", "Architecture", "architecture", "architecture_names",
-    "architecture_of", "load_config", "register_architecture", "unregister_architecture", "Qwen3Config",
+    "architecture_of", "load_config", "register_architecture", "unregister_architecture", "Qwen3Config", "VabelornConfig",
     "preset", "preset_names", "register_preset_folder", "unregister_preset_folder",
 ]

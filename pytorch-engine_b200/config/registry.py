@@ -2,7 +2,7 @@
 
 An architecture is a configuration class and a *plan* function that turns a configuration
 into a ``ModelPlan`` (``parts/spec.py``).  ``config.json``'s ``architectures[0]`` picks the entry
-everywhere: loader, engine, command line and trace replay.  The reference has no registry (it
+(or the string under ``architecture``) everywhere: loader, engine, command line and trace replay.  The reference has no registry (it
 branches on an ``arch`` string and on tensor-name presence, pygguf_engine/model.py:800, 982-1003,
 pygguf_engine/gguf_parser.py:397); this table replaces those branches.
 """
@@ -53,9 +53,14 @@ def architecture_names():
 
 def architecture_of(config_dict: Dict[str, Any]) -> Architecture:
     archs = config_dict.get("architectures")
-    if not archs or not isinstance(archs, (list, tuple)):
-        raise ConfigError("config.json: missing key 'architectures' (a list whose first entry names the model)")
-    return architecture(str(archs[0]))
+    if archs and isinstance(archs, (list, tuple)):
+        return architecture(str(archs[0]))
+    # a file may also name its model in one string under 'architecture'
+    one = config_dict.get("architecture")
+    if isinstance(one, str) and one:
+        return architecture(one)
+    raise ConfigError("config.json: missing key 'architectures' (a list whose first entry names the model) "
+                      "or 'architecture' (its name as a string)")
 
 
 def load_config(folder: str) -> ModelConfig:

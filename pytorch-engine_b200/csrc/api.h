@@ -18,6 +18,12 @@ int pe_attention_generic(int dtype, int decode, const void* q, long long q_ld, v
     const int* seq_past, const int* seq_slot, const int* page_table, int table_stride, int num_pages,
     const void* k_pages, const void* v_pages, float* scratch, int split_keys, int max_splits, int* status,
     cudaStream_t stream);
+int pe_attention_generic_ex(int dtype, int decode, const void* q, long long q_ld, void* out, long long out_ld,
+    int n_seqs, int max_q, int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale, int window, int sink,
+    const float* out_cos, const float* out_sin, int out_rot, int out_rows, int out_inter, const int* seq_qstart,
+    const int* seq_past, const int* seq_slot, const int* page_table, int table_stride, int num_pages,
+    const void* k_pages, const void* v_pages, float* scratch, int split_keys, int max_splits, int* status,
+    cudaStream_t stream);
 int pe_attention_decode_noalloc(int dtype, const void* q, long long q_ld, void* out, long long out_ld, int n_seqs,
     int n_heads, int n_kv_heads, int head_dim, float scale, int window, const int* seq_qstart, const int* seq_past,
     const int* seq_slot, const int* page_table, int table_stride, int num_pages, const void* k_pages,
@@ -69,6 +75,8 @@ int pe_rmsnorm_residual(int dtype, float* residual, const void* delta, const flo
     const int* rows, int n_rows, int dim, float eps, cudaStream_t stream);
 int pe_rmsnorm(int dtype, const void* x, const float* weight, void* out, int n_rows, int dim, float eps,
     cudaStream_t stream);
+int pe_rmsnorm_add(int dtype, float* stream, const void* delta, const float* weight, void* cast, int n_rows, int dim,
+    float eps, cudaStream_t stream_);
 
 // rope_append.cu
 int pe_batch_expand(const int* seq_qstart, const int* seq_past, int n_seqs, int* token_seq, int* token_pos,
@@ -78,6 +86,12 @@ int pe_qk_norm_rope_append(int dtype, void* qkv, long long ld, int n_tokens, int
     const float* sin_table, int rotary_dim, int table_rows, const int* token_seq, const int* token_pos,
     const int* seq_slot, const int* seq_qstart, const int* page_table, int table_stride, int num_pages,
     void* k_pages, void* v_pages, int write_cache, int* status, cudaStream_t stream);
+int pe_qkv_rotate_append(int dtype, void* qkv, long long ld, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+    int v_dim, const float* q_norm_w, const float* k_norm_w, float eps, const float* cos_table, const float* sin_table,
+    int rotary_dim, int table_rows, int interleaved, int v_unit_norm, const float* v_cos, const float* v_sin,
+    int v_rotary_dim, int v_table_rows, int v_interleaved, const int* token_seq, const int* token_pos,
+    const int* seq_slot, const int* seq_qstart, const int* page_table, int table_stride, int num_pages, void* k_pages,
+    void* v_pages, int write_cache, int* status, cudaStream_t stream);
 
 // sampling.cu
 long long pe_sample_scratch_bytes(int n_rows, int vocab, float temperature, int top_k, float top_p, float min_p);
@@ -89,6 +103,21 @@ int pe_repetition_penalty(float* logits, long long ld, int n_rows, int vocab, co
 
 // swiglu.cu
 int pe_silu_mul(int dtype, const void* gate_up, void* out, int n_rows, int inter, cudaStream_t stream);
+
+// token_gate.cu
+int pe_token_gate(int dtype, const void* gx, const void* table, long long table_ld, int col0, const int* tokens,
+    void* out, int n_tokens, int dim, int vocab, int* status, cudaStream_t stream);
+
+// wkv.cu
+int pe_token_shift_mix(int dtype, const void* x, const float* mu, int n_mix, const float* prev_state,
+    const int* token_seq, const int* seq_slot, const int* seq_qstart, void* out, int n_tokens, int width, int n_slots,
+    int* status, cudaStream_t stream);
+int pe_tanh_inplace(int dtype, void* y, long long n, cudaStream_t stream);
+long long pe_wkv_scratch_floats(int n_seqs, int heads, int d, int max_chunks);
+int pe_wkv_recurrence(int dtype, const void* r, const void* k, const void* v, const void* g, long long ld,
+    const float* wlin, const float* w0, const float* u, const float* gnorm, float eps, void* out, float* state,
+    float* prev_state, const void* x, int width, const int* seq_slot, const int* seq_qstart, int n_seqs, int max_q,
+    int heads, int d, int n_slots, int chunk, int max_chunks, float* scratch, int* status, cudaStream_t stream);
 
 // wait_probe.cu
 int pe_wait_probe(unsigned long long* out, int polls, cudaStream_t stream);

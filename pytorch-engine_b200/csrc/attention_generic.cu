@@ -38,35 +38,60 @@ struct AttnArgs {
   float* part_acc;                    // [n_seqs, n_heads, max_splits, head_dim]
   float* part_lse;                    // [n_seqs, n_heads, max_splits]
   int split_keys, max_splits;
+  // what a plain softmax attention does not have (defaults: v_dim = head_dim, the rest off)
+  int v_dim;                          // size of a value row and of a head's output
+  int sink;                           // != 0: one is added to the softmax's denominator (a key of score 0 without a value)
+  const float* out_cos;               // [out_rows, out_rot/2]: the head's output at position p is turned by -angle(p)
+  const float* out_sin;               //   (values were cached turned by their own positions); null: not turned
+  int out_rot, out_rows, out_inter;   // features turned, rows of the tables, layout of pairs (1: 2m with 2m+1)
 };
+
+// Turn a head's output row (float32, in shared or local memory `src`) back by the angle of position `pos` and store it.
+template <typename T>
+__device__ __forceinline__ void store_unrotated(const AttnArgs& a, const float* src, T* dst, int pos, int lane, int nlanes) {
+  const int dv = a.v_dim, half = a.out_rot / 2;
+  const float* cs = a.out_cos + (size_t)pos * half;
+  const float* sn = a.out_sin + (size_t)pos * half;
+  for (int m = lane; m < half; m += nlanes) {
+    const int i0 = a.out_inter ? 2 * m : m, i1 = a.out_inter ? 2 * m + 1 : m + half;
+    const float c = cs[m], s = sn[m];
+    const float x0 = src[i0], x1 = src[i1];
+    dst[i0] = from_f32<T>(x0 * c + x1 * s);     // rotation by the negative angle
+    dst[i1] = from_f32<T>(x1 * c - x0 * s);
+  }
+  for (int c = a.out_rot + lane; c < dv; c += nlanes) dst[c] = from_f32<T>(src[c]);
+}
 
 // Load keys [k0, k0+32) of kv head `kvh` of sequence slot `slot` into shared memory as float32.
 // Rows at or beyond k_end are filled with zeros.  `nthreads` threads starting at `tid` cooperate.
 template <typename T>
 __device__ __forceinline__ void load_tile(const AttnArgs& a, int slot, int kvh, int k0, int k_end, float* Ks,
                                           float* Vs, int tid, int nthreads) {
-  const int d = a.head_dim;
+  const int d = a.head_dim, dv = a.v_dim;
   const int logical = k0 / kPageTokens;
   int page = -1;
   if (logical < a.table_stride) page = a.page_table[(size_t)slot * a.table_stride + logical];
   const bool ok = page >= 0 && page < a.num_pages;
   if (!ok && tid == 0 && k0 < k_end) report(a.status, kStatusPageOutOfRange, slot, page, k0);
-  const size_t base = (((size_t)(ok ? page : 0) * a.n_kv_heads + kvh) * kPageTokens + (k0 % kPageTokens)) * d;
-  const T* kp = (const T*)a.k_pages + base;
-  const T* vp = (const T*)a.v_pages + base;
-  const int total = kTileKeys * d;
-  for (int i = tid; i < total; i += nthreads) {
+  const size_t base = ((size_t)(ok ? page : 0) * a.n_kv_heads + kvh) * kPageTokens + (k0 % kPageTokens);
+  const T* kp = (const T*)a.k_pages + base * d;
+  const T* vp = (const T*)a.v_pages + base * dv;
+  for (int i = tid; i < kTileKeys * d; i += nthreads) {
     const int r = i / d, c = i - r * d;
     const bool live = ok && (k0 + r) < k_end;
     Ks[r * (d + 1) + c] = live ? to_f32<T>(kp[i]) : 0.f;
-    Vs[r * d + c] = live ? to_f32<T>(vp[i]) : 0.f;
+  }
+  for (int i = tid; i < kTileKeys * dv; i += nthreads) {
+    const int r = i / dv;
+    const bool live = ok && (k0 + r) < k_end;
+    Vs[i] = live ? to_f32<T>(vp[i]) : 0.f;
   }
 }
 
 // One warp: fold the 32 keys of the tile in shared memory into (m, l, acc) of its query heads.
 // `visible` says whether this lane's key takes part for this warp's query.
 template <int DPL>
-__device__ __forceinline__ void fold_tile(const float* qs /*[kGT][d]*/, const float* Ks, const float* Vs, int d,
+__device__ __forceinline__ void fold_tile(const float* qs /*[kGT][d]*/, const float* Ks, const float* Vs, int d, int dv,
                                           int n_heads_here, float scale, bool visible, int lane, float (&m)[kGT],
                                           float (&l)[kGT], float (&acc)[kGT][DPL]) {
   float s[kGT];
@@ -98,11 +123,11 @@ __device__ __forceinline__ void fold_tile(const float* qs /*[kGT][d]*/, const fl
     float pj[kGT];
 #pragma unroll
     for (int h = 0; h < kGT; ++h) pj[h] = __shfl_sync(0xffffffffu, p[h], j);
-    const float* vrow = Vs + j * d;
+    const float* vrow = Vs + j * dv;
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
       const int c = lane + 32 * i;
-      const float v = (c < d) ? vrow[c] : 0.f;
+      const float v = (c < dv) ? vrow[c] : 0.f;
 #pragma unroll
       for (int h = 0; h < kGT; ++h) acc[h][i] = fmaf(pj[h], v, acc[h][i]);
     }
@@ -117,10 +142,11 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(AttnArgs a) {
   pdl_wait_block();
   pdl_launch_dependents();
   constexpr int W = 8;
-  const int d = a.head_dim;
+  const int d = a.head_dim, dv = a.v_dim;
+  const int qrow = max(d, dv);               // a warp's q rows are used again to stage its output rows
   float* Ks = smem;                          // [32][d+1]
-  float* Vs = Ks + kTileKeys * (d + 1);      // [32][d]
-  float* Qs = Vs + kTileKeys * d;            // [W][kGT][d]
+  float* Vs = Ks + kTileKeys * (d + 1);      // [32][dv]
+  float* Qs = Vs + kTileKeys * dv;           // [W][kGT][max(d, dv)]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z;
   const int group = a.n_heads / a.n_kv_heads;
@@ -137,7 +163,7 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(AttnArgs a) {
   const int qpos = past + my_row;
   const int last_pos = past + min(q_len, first + W) - 1;
   // q of this warp into shared memory
-  float* qs = Qs + warp * kGT * d;
+  float* qs = Qs + warp * kGT * qrow;
   for (int i = lane; i < kGT * d; i += 32) {
     const int h = i / d, c = i - h * d;
     float v = 0.f;
@@ -164,18 +190,35 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(AttnArgs a) {
     bool visible = kpos <= qpos;
     if (a.window > 0) visible = visible && (kpos > qpos - a.window);
     if (a.window > 0 && k0 + kTileKeys - 1 <= qpos - a.window) continue;  // whole tile before the window
-    fold_tile<DPL>(qs, Ks, Vs, d, n_here, a.scale, visible, lane, m, l, acc);
+    fold_tile<DPL>(qs, Ks, Vs, d, dv, n_here, a.scale, visible, lane, m, l, acc);
   }
   if (!active) return;
+  if (a.out_cos && (qpos < 0 || qpos >= a.out_rows)) {
+    if (lane == 0) report(a.status, kStatusPositionOutOfRange, q0 + my_row, qpos, a.out_rows);
+    return;
+  }
 #pragma unroll
   for (int h = 0; h < kGT; ++h) {
     if (h >= n_here) continue;
-    const float inv = 1.f / fmaxf(l[h], 1e-20f);
-    T* o = (T*)a.out + (size_t)(q0 + my_row) * a.out_ld + (size_t)(h0 + h) * d;
+    // the sink: a key of score 0 that every query sees and that carries no value
+    const float denom = l[h] + (a.sink ? expf(-m[h]) : 0.f);
+    const float inv = 1.f / fmaxf(denom, 1e-20f);
+    T* o = (T*)a.out + (size_t)(q0 + my_row) * a.out_ld + (size_t)(h0 + h) * dv;
+    if (a.out_cos) {
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        const int c = lane + 32 * i;
+        if (c < dv) qs[c] = acc[h][i] * inv;
+      }
+      __syncwarp();
+      store_unrotated<T>(a, qs, o, qpos, lane, 32);
+      continue;
+    }
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
       const int c = lane + 32 * i;
-      if (c < d) o[c] = from_f32<T>(acc[h][i] * inv);
+      if (c < dv) o[c] = from_f32<T>(acc[h][i] * inv);
     }
   }
 }
@@ -187,14 +230,14 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_split_kernel(AttnArgs a) 
   extern __shared__ float smem[];
   pdl_wait_block();
   pdl_launch_dependents();
-  const int d = a.head_dim;
+  const int d = a.head_dim, dv = a.v_dim;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int per_warp = kTileKeys * (d + 1) + kTileKeys * d;
+  const int per_warp = kTileKeys * (d + 1) + kTileKeys * dv;
   float* Ks = smem + warp * per_warp;
   float* Vs = Ks + kTileKeys * (d + 1);
   float* Qs = smem + NW * per_warp;              // [kGT][d], shared by the warps
   float* Ms = Qs + kGT * d;                      // [NW][kGT] m, then [NW][kGT] l
-  float* Acc = Ms + 2 * NW * kGT;                // [NW][kGT][d]
+  float* Acc = Ms + 2 * NW * kGT;                // [NW][kGT][dv]
   const int b = blockIdx.z, split = blockIdx.x;
   const int group = a.n_heads / a.n_kv_heads;
   const int chunks = (group + kGT - 1) / kGT;
@@ -230,7 +273,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_split_kernel(AttnArgs a) 
     __syncwarp();
     const int kpos = k0 + lane;
     const bool visible = kpos >= max(k_lo, win_lo) && kpos < k_hi;
-    fold_tile<DPL>(Qs, Ks, Vs, d, n_here, a.scale, visible, lane, m, l, acc);
+    fold_tile<DPL>(Qs, Ks, Vs, d, dv, n_here, a.scale, visible, lane, m, l, acc);
     __syncwarp();
   }
   // merge the warps (fixed order: warp 0, 1, ..)
@@ -246,11 +289,11 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_split_kernel(AttnArgs a) 
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
       const int c = lane + 32 * i;
-      if (c < d) Acc[(warp * kGT + h) * d + c] = acc[h][i];
+      if (c < dv) Acc[(warp * kGT + h) * dv + c] = acc[h][i];
     }
   __syncthreads();
-  for (int i = threadIdx.x; i < n_here * d; i += blockDim.x) {
-    const int h = i / d, c = i - h * d;
+  for (int i = threadIdx.x; i < n_here * dv; i += blockDim.x) {
+    const int h = i / dv, c = i - h * dv;
     float mm = -INFINITY;
     for (int w = 0; w < NW; ++w) mm = fmaxf(mm, Ms[w * kGT + h]);
     float ll = 0.f, aa = 0.f;
@@ -259,11 +302,11 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_split_kernel(AttnArgs a) 
         const float mw = Ms[w * kGT + h];
         const float f = (mw == -INFINITY) ? 0.f : expf(mw - mm);
         ll += Ms[NW * kGT + w * kGT + h] * f;
-        aa += Acc[(w * kGT + h) * d + c] * f;
+        aa += Acc[(w * kGT + h) * dv + c] * f;
       }
     }
     const size_t pidx = ((size_t)b * a.n_heads + (h0 + h)) * a.max_splits + split;
-    a.part_acc[pidx * d + c] = (ll > 0.f) ? aa / ll : 0.f;
+    a.part_acc[pidx * dv + c] = (ll > 0.f) ? aa / ll : 0.f;
     if (c == 0) a.part_lse[pidx] = (ll > 0.f) ? mm + logf(ll) : -INFINITY;
   }
 }
@@ -273,8 +316,9 @@ template <typename T>
 __global__ void attn_decode_combine_kernel(AttnArgs a) {
   pdl_wait_block();
   pdl_launch_dependents();
+  extern __shared__ float orow[];   // v_dim floats when the output is turned back
   const int b = blockIdx.y, h = blockIdx.x;
-  const int d = a.head_dim;
+  const int d = a.v_dim;
   const int t = a.seq_qstart[b];
   const int len = a.seq_past[b] + 1;
   int n_splits = (len + a.split_keys - 1) / a.split_keys;
@@ -287,9 +331,9 @@ __global__ void attn_decode_combine_kernel(AttnArgs a) {
   const int win_lo = a.window > 0 ? max(0, len - a.window) : 0;
   const int first = min(win_lo / a.split_keys, n_splits);
   const size_t base = ((size_t)b * a.n_heads + h) * a.max_splits;
-  float mx = -INFINITY;
+  float mx = a.sink ? 0.f : -INFINITY;   // the sink is one more range whose log-sum is 0 and whose output is 0
   for (int s = first; s < n_splits; ++s) mx = fmaxf(mx, a.part_lse[base + s]);
-  float denom = 0.f;
+  float denom = a.sink ? expf(-mx) : 0.f;
   for (int s = first; s < n_splits; ++s) {
     const float e = a.part_lse[base + s];
     denom += (e == -INFINITY) ? 0.f : expf(e - mx);
@@ -303,7 +347,17 @@ __global__ void attn_decode_combine_kernel(AttnArgs a) {
       const float w = (e == -INFINITY) ? 0.f : expf(e - mx) * inv;
       v = fmaf(w, a.part_acc[(base + s) * d + c], v);
     }
-    o[c] = from_f32<T>(v);
+    if (a.out_cos) orow[c] = v;
+    else o[c] = from_f32<T>(v);
+  }
+  if (a.out_cos) {
+    const int qpos = len - 1;
+    if (qpos < 0 || qpos >= a.out_rows) {
+      if (threadIdx.x == 0) report(a.status, kStatusPositionOutOfRange, t, qpos, a.out_rows);
+      return;
+    }
+    __syncthreads();
+    store_unrotated<T>(a, orow, o, qpos, threadIdx.x, blockDim.x);
   }
 }
 
@@ -319,8 +373,8 @@ static int opt_in_smem(K kernel, size_t bytes) {
 
 template <typename T, int DPL>
 static int launch_prefill(const AttnArgs& a, int n_seqs, int max_q, cudaStream_t stream) {
-  const int d = a.head_dim;
-  const size_t smem = ((size_t)kTileKeys * (d + 1) + (size_t)kTileKeys * d + (size_t)8 * kGT * d) * sizeof(float);
+  const int d = a.head_dim, dv = a.v_dim;
+  const size_t smem = ((size_t)kTileKeys * (d + 1) + (size_t)kTileKeys * dv + (size_t)8 * kGT * (d > dv ? d : dv)) * sizeof(float);
   auto k = attn_prefill_kernel<T, DPL>;
   int e = opt_in_smem(k, smem);
   if (e) return e;
@@ -334,9 +388,9 @@ static int launch_prefill(const AttnArgs& a, int n_seqs, int max_q, cudaStream_t
 
 template <typename T, int DPL, int NW>
 static int launch_decode(const AttnArgs& a, int n_seqs, cudaStream_t stream) {
-  const int d = a.head_dim;
-  const size_t smem = ((size_t)NW * (kTileKeys * (d + 1) + kTileKeys * d) + (size_t)kGT * d + 2 * NW * kGT +
-                       (size_t)NW * kGT * d) * sizeof(float);
+  const int d = a.head_dim, dv = a.v_dim;
+  const size_t smem = ((size_t)NW * (kTileKeys * (d + 1) + kTileKeys * dv) + (size_t)kGT * d + 2 * NW * kGT +
+                       (size_t)NW * kGT * dv) * sizeof(float);
   auto k = attn_decode_split_kernel<T, DPL, NW>;
   int e = opt_in_smem(k, smem);
   if (e) return e;
@@ -346,15 +400,15 @@ static int launch_decode(const AttnArgs& a, int n_seqs, cudaStream_t stream) {
   pe::launch(k, grid, NW * 32, smem, stream, a);
   PE_LAUNCH_CHECK();
   dim3 cgrid(a.n_heads, n_seqs);
-  pe::launch(attn_decode_combine_kernel<T>, cgrid, 128, 0, stream, a);
+  pe::launch(attn_decode_combine_kernel<T>, cgrid, 128, a.out_cos ? (size_t)dv * sizeof(float) : 0, stream, a);
   PE_LAUNCH_CHECK();
   return PE_OK;
 }
 
 template <typename T>
 static int dispatch(const AttnArgs& a, int n_seqs, int max_q, bool decode, cudaStream_t stream) {
-  const int d = a.head_dim;
-  if (d > 512) return PE_ERR_UNSUPPORTED_SIZE;
+  if (a.head_dim > 512 || a.v_dim > 512) return PE_ERR_UNSUPPORTED_SIZE;
+  const int d = a.v_dim;   // output features per lane
   if (decode) {
     if (d <= 32) return launch_decode<T, 1, 4>(a, n_seqs, stream);
     if (d <= 64) return launch_decode<T, 2, 4>(a, n_seqs, stream);
@@ -383,9 +437,27 @@ extern "C" int pe_attention_generic(int dtype, int decode, const void* q, long l
                                     const int* page_table, int table_stride, int num_pages, const void* k_pages,
                                     const void* v_pages, float* scratch, int split_keys, int max_splits, int* status,
                                     cudaStream_t stream) {
+  return pe_attention_generic_ex(dtype, decode, q, q_ld, out, out_ld, n_seqs, max_q, n_heads, n_kv_heads, head_dim,
+                                 head_dim, scale, window, 0, nullptr, nullptr, 0, 0, 0, seq_qstart, seq_past, seq_slot,
+                                 page_table, table_stride, num_pages, k_pages, v_pages, scratch, split_keys, max_splits,
+                                 status, stream);
+}
+
+// The same with values of a size of their own (`v_dim`; the scratch then holds v_dim floats per partial row), a sink
+// in the softmax, and the output turned back by the query's position (tables [out_rows, out_rot/2]).
+extern "C" int pe_attention_generic_ex(int dtype, int decode, const void* q, long long q_ld, void* out, long long out_ld,
+                                       int n_seqs, int max_q, int n_heads, int n_kv_heads, int head_dim, int v_dim,
+                                       float scale, int window, int sink, const float* out_cos, const float* out_sin,
+                                       int out_rot, int out_rows, int out_inter, const int* seq_qstart,
+                                       const int* seq_past, const int* seq_slot, const int* page_table, int table_stride,
+                                       int num_pages, const void* k_pages, const void* v_pages, float* scratch,
+                                       int split_keys, int max_splits, int* status, cudaStream_t stream) {
   if (n_seqs <= 0) return PE_OK;
-  if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || n_heads % n_kv_heads) return PE_ERR_BAD_ARGUMENT;
+  if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || v_dim <= 0 || n_heads % n_kv_heads) return PE_ERR_BAD_ARGUMENT;
+  if (out_cos && (!out_sin || out_rot <= 0 || out_rot > v_dim || (out_rot & 1))) return PE_ERR_BAD_ARGUMENT;
   pe::AttnArgs a;
+  a.v_dim = v_dim; a.sink = sink; a.out_cos = out_cos; a.out_sin = out_sin;
+  a.out_rot = out_cos ? out_rot : 0; a.out_rows = out_rows; a.out_inter = out_inter;
   a.q = q; a.q_ld = q_ld; a.out = out; a.out_ld = out_ld;
   a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.head_dim = head_dim; a.scale = scale; a.window = window;
   a.seq_qstart = seq_qstart; a.seq_past = seq_past; a.seq_slot = seq_slot;
@@ -396,7 +468,7 @@ extern "C" int pe_attention_generic(int dtype, int decode, const void* q, long l
     if (!scratch || split_keys <= 0 || split_keys % pe::kTileKeys || max_splits <= 0) return PE_ERR_BAD_ARGUMENT;
     a.split_keys = split_keys; a.max_splits = max_splits;
     a.part_acc = scratch;
-    a.part_lse = scratch + (size_t)n_seqs * n_heads * max_splits * head_dim;
+    a.part_lse = scratch + (size_t)n_seqs * n_heads * max_splits * v_dim;
   }
   if (dtype == PE_F32) return pe::dispatch<float>(a, n_seqs, max_q, decode != 0, stream);
   if (dtype == PE_BF16) return pe::dispatch<__nv_bfloat16>(a, n_seqs, max_q, decode != 0, stream);
@@ -459,6 +531,7 @@ extern "C" int pe_attention_decode_noalloc(int dtype, const void* q, long long q
   a.page_table = page_table; a.table_stride = table_stride; a.num_pages = num_pages;
   a.k_pages = k_pages; a.v_pages = v_pages; a.status = status;
   a.split_keys = split_keys; a.max_splits = max_splits;
+  a.v_dim = head_dim; a.sink = 0; a.out_cos = nullptr; a.out_sin = nullptr; a.out_rot = 0; a.out_rows = 0; a.out_inter = 0;
   a.part_acc = scratch;
   a.part_lse = scratch + (size_t)n_seqs * n_heads * max_splits * head_dim;
   if (dtype == PE_F32) return pe::dispatch<float>(a, n_seqs, 1, true, stream);

@@ -128,6 +128,34 @@ __global__ void rmsnorm_plain_kernel(const T* x, const float* __restrict__ weigh
     out[(size_t)r * dim + c] = from_f32<T>(row_buf[c] * inv * weight[c]);
 }
 
+// Norm on a sublayer's output, then the residual add (a block that norms what it adds, not what it reads):
+//   stream[row] += delta[row] * rsqrt(mean(delta[row]^2) + eps) * w        float32
+// and, when `cast` is given, cast[row] = stream[row] in the run dtype: the next sublayer's input.
+template <typename T>
+__global__ void rmsnorm_add_kernel(float* __restrict__ stream, const T* delta, const float* __restrict__ weight,
+                                   T* __restrict__ cast, int n_rows, int dim, float eps) {
+  extern __shared__ float row_buf[];  // dim floats
+  __shared__ float red[32];
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  if (r >= n_rows) return;
+  const T* d_row = delta + (size_t)r * dim;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    const float y = to_f32<T>(d_row[c]);
+    row_buf[c] = y;
+    ss += y * y;
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)dim + eps);
+  float* s_row = stream + (size_t)r * dim;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    const float h = s_row[c] + row_buf[c] * inv * weight[c];
+    s_row[c] = h;
+    if (cast) cast[(size_t)r * dim + c] = from_f32<T>(h);
+  }
+}
+
 template <typename K>
 static int set_smem(K kernel, size_t bytes) {
   if (bytes > 48 * 1024) {
@@ -184,6 +212,29 @@ extern "C" int pe_rmsnorm(int dtype, const void* x, const float* weight, void* o
     auto k = pe::rmsnorm_plain_kernel<__nv_bfloat16>;
     if ((e = pe::set_smem(k, smem))) return e;
     pe::launch(k, n_rows, threads, smem, stream, (const __nv_bfloat16*)x, weight, (__nv_bfloat16*)out, n_rows, dim, eps);
+  } else {
+    return PE_ERR_UNSUPPORTED_DTYPE;
+  }
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}
+
+extern "C" int pe_rmsnorm_add(int dtype, float* stream, const void* delta, const float* weight, void* cast, int n_rows,
+                              int dim, float eps, cudaStream_t stream_) {
+  if (n_rows <= 0) return PE_OK;
+  if (dim <= 0) return PE_ERR_BAD_ARGUMENT;
+  const size_t smem = (size_t)dim * sizeof(float);
+  if (smem > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;
+  const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+  int e;
+  if (dtype == PE_F32) {
+    auto k = pe::rmsnorm_add_kernel<float>;
+    if ((e = pe::set_smem(k, smem))) return e;
+    pe::launch(k, n_rows, threads, smem, stream_, stream, (const float*)delta, weight, (float*)cast, n_rows, dim, eps);
+  } else if (dtype == PE_BF16) {
+    auto k = pe::rmsnorm_add_kernel<__nv_bfloat16>;
+    if ((e = pe::set_smem(k, smem))) return e;
+    pe::launch(k, n_rows, threads, smem, stream_, stream, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)cast, n_rows, dim, eps);
   } else {
     return PE_ERR_UNSUPPORTED_DTYPE;
   }

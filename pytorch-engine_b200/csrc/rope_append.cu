@@ -369,6 +369,116 @@ __global__ void __launch_bounds__(256, 4) qk_norm_rope_append_vec8_kernel(RopeAp
   }
 }
 
+// ---- the general form -------------------------------------------------------------------------------------------
+// Queries and keys: optional RMS norm with a weight, then rotation of the first `rotary_dim` features in either
+// layout of pairs (split-half: j with j + rotary_dim/2; interleaved: 2j with 2j + 1), angle tables by position (a
+// table may carry a factor on cos and sin).  Values, of a size of their own: optionally divided by their root mean
+// square (no weight), optionally rotated by their position over `v_rotary_dim` features with tables of their own;
+// they go to the cache so.  One warp per (token, head), float32 arithmetic, any sizes.
+struct QkvRotateArgs {
+  void* qkv; long long ld;        // a row: q heads x head_dim | k heads x head_dim | v heads x v_dim
+  int n_tokens, n_heads, n_kv_heads, head_dim, v_dim;
+  const float* q_norm_w; const float* k_norm_w; float eps;
+  const float* cos_table; const float* sin_table; int rotary_dim, table_rows, interleaved;
+  int v_unit_norm;
+  const float* v_cos; const float* v_sin; int v_rotary_dim, v_table_rows, v_interleaved;
+  const int* token_seq; const int* token_pos; const int* seq_slot; const int* seq_qstart;
+  const int* page_table; int table_stride, num_pages;
+  void* k_pages; void* v_pages;   // [num_pages, n_kv_heads, 64, head_dim] and [.., v_dim]
+  int write_cache;
+  int* status;
+};
+
+template <typename T>
+__global__ void qkv_rotate_append_kernel(QkvRotateArgs a) {
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+  const int total_heads = a.n_heads + 2 * a.n_kv_heads;
+  const bool valid = t < a.n_tokens && head < total_heads;
+  const bool is_q = head < a.n_heads;
+  const bool is_k = !is_q && head < a.n_heads + a.n_kv_heads;
+  const bool is_v = !is_q && !is_k;
+  const int kv_head = is_q ? -1 : (is_k ? head - a.n_heads : head - a.n_heads - a.n_kv_heads);
+  const int D = is_v ? a.v_dim : a.head_dim;
+  const bool to_cache = valid && !is_q && a.write_cache;
+  // the batch description and the page table do not come from the kernel before this one
+  int pos = 0, seq = 0, slot = 0, q_begin = 0, q_end = 0, page = -1;
+  if (valid) pos = a.token_pos[t];
+  if (to_cache) {
+    seq = a.token_seq[t];
+    slot = a.seq_slot[seq];
+    q_begin = a.seq_qstart[seq];
+    q_end = a.seq_qstart[seq + 1];
+    if (pos >= 0 && pos / kPageTokens < a.table_stride)
+      page = a.page_table[(size_t)slot * a.table_stride + pos / kPageTokens];
+  }
+  pdl_wait_block();
+  pdl_launch_dependents();
+  if (!valid) return;
+  const size_t row_off = is_v ? (size_t)(a.n_heads + a.n_kv_heads) * a.head_dim + (size_t)kv_head * a.v_dim
+                              : (size_t)head * a.head_dim;
+  T* row = (T*)a.qkv + (size_t)t * a.ld + row_off;
+  T* cache_row = nullptr;
+  if (to_cache) {
+    if (pos < 0 || pos / kPageTokens >= a.table_stride) {
+      if (lane == 0) report(a.status, kStatusPositionOutOfRange, t, pos, a.table_stride * kPageTokens);
+    } else if (page < 0 || page >= a.num_pages) {
+      if (lane == 0) report(a.status, kStatusPageOutOfRange, t, page, a.num_pages);
+    } else {
+      T* base = (T*)(is_k ? a.k_pages : a.v_pages);
+      const int off = pos % kPageTokens;
+      cache_row = base + (((size_t)page * a.n_kv_heads + kv_head) * kPageTokens + off) * D;
+      // rows of a page beyond the sequence's last key must hold finite values (see the kernel above)
+      if (t + 1 == q_end && off + 1 < kPageTokens && (off == 0 || q_end - q_begin > 1)) {
+        T* rest = cache_row + D;
+        const size_t n = (size_t)(kPageTokens - 1 - off) * D;
+        for (size_t i = lane; i < n; i += 32) rest[i] = from_f32<T>(0.f);
+      }
+    }
+  }
+  const float* w = is_q ? a.q_norm_w : (is_k ? a.k_norm_w : nullptr);
+  const bool normed = is_v ? (a.v_unit_norm != 0) : (w != nullptr);
+  float inv = 1.f;
+  if (normed) {
+    float ss = 0.f;
+    for (int c = lane; c < D; c += 32) {
+      const float x = to_f32<T>(row[c]);
+      ss += x * x;
+    }
+    inv = rsqrtf(warp_sum(ss) / (float)D + a.eps);
+  }
+  const float* ct = is_v ? a.v_cos : a.cos_table;
+  const float* st = is_v ? a.v_sin : a.sin_table;
+  const int rot = ct ? (is_v ? a.v_rotary_dim : a.rotary_dim) : 0;
+  const int rows = is_v ? a.v_table_rows : a.table_rows;
+  const bool inter = (is_v ? a.v_interleaved : a.interleaved) != 0;
+  const int half = rot / 2;
+  if (rot > 0 && (pos < 0 || pos >= rows)) {
+    if (lane == 0) report(a.status, kStatusPositionOutOfRange, t, pos, rows);
+    return;
+  }
+  auto value = [&](int c) -> float {
+    float x = to_f32<T>(row[c]);
+    if (normed) x *= inv;
+    if (w) x *= w[c];
+    return x;
+  };
+  auto put = [&](int c, float x) {
+    const T o = from_f32<T>(x);
+    if (!is_v) row[c] = o;
+    if (cache_row) cache_row[c] = o;
+  };
+  for (int j = lane; j < half; j += 32) {
+    const int i0 = inter ? 2 * j : j, i1 = inter ? 2 * j + 1 : j + half;
+    const float x0 = value(i0), x1 = value(i1);
+    const float c = ct[(size_t)pos * half + j], s = st[(size_t)pos * half + j];
+    put(i0, x0 * c - x1 * s);
+    put(i1, x1 * c + x0 * s);
+  }
+  for (int c = rot + lane; c < D; c += 32) put(c, value(c));
+}
+
 }  // namespace pe
 
 extern "C" int pe_batch_expand(const int* seq_qstart, const int* seq_past, int n_seqs, int* token_seq, int* token_pos,
@@ -427,6 +537,39 @@ extern "C" int pe_qk_norm_rope_append(int dtype, void* qkv, long long ld, int n_
     else pe::launch(pe::qk_norm_rope_append_kernel<__nv_bfloat16, false>, grid, warps * 32, 0, stream, a);
   } else
     return PE_ERR_UNSUPPORTED_DTYPE;
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}
+
+extern "C" int pe_qkv_rotate_append(int dtype, void* qkv, long long ld, int n_tokens, int n_heads, int n_kv_heads,
+                                    int head_dim, int v_dim, const float* q_norm_w, const float* k_norm_w, float eps,
+                                    const float* cos_table, const float* sin_table, int rotary_dim, int table_rows,
+                                    int interleaved, int v_unit_norm, const float* v_cos, const float* v_sin,
+                                    int v_rotary_dim, int v_table_rows, int v_interleaved, const int* token_seq,
+                                    const int* token_pos, const int* seq_slot, const int* seq_qstart,
+                                    const int* page_table, int table_stride, int num_pages, void* k_pages,
+                                    void* v_pages, int write_cache, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return PE_OK;
+  if (head_dim <= 0 || v_dim <= 0 || n_heads <= 0 || n_kv_heads < 0) return PE_ERR_BAD_ARGUMENT;
+  if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return PE_ERR_UNSUPPORTED_SIZE;
+  if (v_rotary_dim < 0 || v_rotary_dim > v_dim || (v_rotary_dim & 1)) return PE_ERR_UNSUPPORTED_SIZE;
+  if (ld < (long long)(n_heads + n_kv_heads) * head_dim + (long long)n_kv_heads * v_dim) return PE_ERR_BAD_ARGUMENT;
+  pe::QkvRotateArgs a;
+  a.qkv = qkv; a.ld = ld; a.n_tokens = n_tokens; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.head_dim = head_dim;
+  a.v_dim = v_dim; a.q_norm_w = q_norm_w; a.k_norm_w = k_norm_w; a.eps = eps;
+  a.cos_table = cos_table; a.sin_table = sin_table; a.rotary_dim = cos_table ? rotary_dim : 0; a.table_rows = table_rows;
+  a.interleaved = interleaved; a.v_unit_norm = v_unit_norm;
+  a.v_cos = v_cos; a.v_sin = v_sin; a.v_rotary_dim = v_cos ? v_rotary_dim : 0; a.v_table_rows = v_table_rows;
+  a.v_interleaved = v_interleaved;
+  a.token_seq = token_seq; a.token_pos = token_pos; a.seq_slot = seq_slot; a.seq_qstart = seq_qstart;
+  a.page_table = page_table; a.table_stride = table_stride; a.num_pages = num_pages;
+  a.k_pages = k_pages; a.v_pages = v_pages; a.write_cache = write_cache; a.status = status;
+  const int warps = 4;
+  dim3 grid(n_tokens, (n_heads + 2 * n_kv_heads + warps - 1) / warps);
+  if (grid.y > 65535) return PE_ERR_UNSUPPORTED_SIZE;
+  if (dtype == PE_F32) pe::launch(pe::qkv_rotate_append_kernel<float>, grid, warps * 32, 0, stream, a);
+  else if (dtype == PE_BF16) pe::launch(pe::qkv_rotate_append_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream, a);
+  else return PE_ERR_UNSUPPORTED_DTYPE;
   PE_LAUNCH_CHECK();
   return PE_OK;
 }

@@ -100,14 +100,15 @@ class Engine:
         arch = architecture(config.architecture)
         self.plan = arch.plan(config)
         self.runtime = Runtime(self.device, self.dtype)
-        if weights is None:
-            weights = load_weights(model_path, self.plan, device=self.device, dtype=self.dtype)
-        self.model = DecoderModel(self.plan, weights, self.runtime)
-        del weights
         self.max_context_len = int(max_context_len or config.max_positions)
         if self.max_context_len > config.max_positions:
             raise ValueError(f"max_context_len {self.max_context_len} exceeds the model's max_position_embeddings "
                              f"{config.max_positions}")
+        self.runtime.position_limit = self.max_context_len   # position tables need no more rows than a sequence can have
+        if weights is None:
+            weights = load_weights(model_path, self.plan, device=self.device, dtype=self.dtype)
+        self.model = DecoderModel(self.plan, weights, self.runtime)
+        del weights
         self.max_batch = int(max_batch)
         if max_cache_tokens is None:
             max_cache_tokens = self.default_cache_tokens(self.max_batch, self.max_context_len,
@@ -138,7 +139,7 @@ class Engine:
         """``max_batch`` sequences of full length, but no more tokens than fit in four fifths of the
         device memory that is free now (whole pages; at least one page)."""
         want = max_batch * pages_for(max_context_len) * PAGE_TOKENS
-        per_token = sum(2 * r.kv_heads * r.head_dim for r in requests.values() if r is not None and r.kind == "kv")
+        per_token = sum(r.kv_heads * (r.head_dim + r.value_dim) for r in requests.values() if r is not None and r.kind == "kv")
         per_token *= torch.empty((), dtype=dtype).element_size()
         if per_token == 0:
             return want

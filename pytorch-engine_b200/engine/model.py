@@ -95,6 +95,7 @@ class DecoderModel:
         rt = self.runtime
         stream = ctx.buffer("model.stream", (ctx.n_tokens, self.hidden), torch.float32)
         self.embedding.forward(ctx.tokens, stream)
+        ctx.stream_copy = None    # a copy of the stream in the run dtype, if a block has left one (post-norm blocks do)
         pending = None
         for run in self.plan.order:
             view = self._view(cache, run)

@@ -61,10 +61,20 @@ _SIGNATURES = {
     "pe_attention_umma_prefill": [P, L, L, P, L, I, I, I, I, I, F, I, P, P, P, P, I, I, P, P, I, P, P, P],
     "pe_attention_umma_supported": [I, I, I],
     "pe_wait_probe": [P, I, P],
+    "pe_rmsnorm_add": [I, P, P, P, P, I, I, F, P],
+    "pe_token_gate": [I, P, P, L, I, P, P, I, I, I, P, P],
+    "pe_token_shift_mix": [I, P, P, I, P, P, P, P, P, I, I, I, P, P],
+    "pe_tanh_inplace": [I, P, L, P],
+    "pe_wkv_recurrence": [I, P, P, P, P, L, P, P, P, P, F, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P, P, P],
+    "pe_qkv_rotate_append": [I, P, L, I, I, I, I, I, P, P, F, P, P, I, I, I, I, P, P, I, I, I, P, P, P, P, P, I, I, P, P,
+                             I, P, P],
+    "pe_attention_generic_ex": [I, I, P, L, P, L, I, I, I, I, I, I, F, I, I, P, P, I, I, I, P, P, P, P, I, I, P, P, P,
+                                I, I, P, P],
     "pe_attention_decode_noalloc": [I, P, L, P, L, I, I, I, I, F, I, P, P, P, P, I, I, P, P, I, I, P, P],
 }
 _RESTYPES = {"pe_wait_limit_polls": (L, []),
              "pe_attention_generic_scratch_floats": (L, [I, I, I, I]),
+             "pe_wkv_scratch_floats": (L, [I, I, I, I]),
              "pe_sample_scratch_bytes": (L, [I, I, F, I, F, F])}
 
 

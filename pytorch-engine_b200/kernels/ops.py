@@ -145,6 +145,135 @@ def attention_generic(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: 
     _count(2 if decode else 1)
 
 
+def attention_generic_ex(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_q: int, n_heads: int,
+                         n_kv_heads: int, head_dim: int, v_dim: int, scale: float, window: int, sink: bool,
+                         out_cos: Optional[torch.Tensor], out_sin: Optional[torch.Tensor], out_rot: int,
+                         out_interleaved: bool, seq_qstart: torch.Tensor, seq_past: torch.Tensor, seq_slot: torch.Tensor,
+                         page_table: torch.Tensor, num_pages: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                         scratch: Optional[torch.Tensor], split_keys: int, max_splits: int, status: torch.Tensor) -> None:
+    """``attention_generic`` with values of their own size ``v_dim`` (``out`` rows hold ``n_heads * v_dim``
+    features; decode scratch: ``attention_generic_scratch_floats(.., v_dim, ..)``), optionally a sink in the
+    softmax (one added to its denominator) and the output of each head turned back by the query's position
+    (angle tables ``out_cos, out_sin [rows, out_rot / 2]``, pairs interleaved or split-half)."""
+    _need(q.stride(-1) == 1 and out.stride(-1) == 1, "attention: rows must be contiguous")
+    _need(q.dtype == out.dtype == k_pages.dtype == v_pages.dtype, "attention: q, out and the cache must share a dtype")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous(), "attention: pages must be contiguous")
+    if out_cos is not None:
+        _need(out_cos.dtype == torch.float32 and out_sin.dtype == torch.float32 and out_cos.shape == out_sin.shape
+              and out_cos.shape[1] * 2 == out_rot and out_cos.is_contiguous() and out_sin.is_contiguous(),
+              "attention: the output's angle tables are float32 [rows, out_rot / 2]")
+    check(library().pe_attention_generic_ex(
+        dtype_tag(q.dtype), 1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), n_seqs, max_q,
+        n_heads, n_kv_heads, head_dim, v_dim, float(scale), int(window), 1 if sink else 0, _ptr(out_cos), _ptr(out_sin),
+        int(out_rot) if out_cos is not None else 0, 0 if out_cos is None else out_cos.shape[0],
+        1 if out_interleaved else 0, _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot), _ptr(page_table),
+        page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages), _ptr(scratch), split_keys, max_splits,
+        _ptr(status), _stream()), "attention_generic_ex")
+    _count(2 if decode else 1)
+
+
+def qkv_rotate_append(qkv: torch.Tensor, n_tokens: int, n_heads: int, n_kv_heads: int, head_dim: int, v_dim: int,
+                      q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
+                      cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int, interleaved: bool,
+                      v_unit_norm: bool, v_cos: Optional[torch.Tensor], v_sin: Optional[torch.Tensor], v_rotary_dim: int,
+                      v_interleaved: bool, token_seq: torch.Tensor, token_pos: torch.Tensor, seq_slot: torch.Tensor,
+                      seq_qstart: torch.Tensor, page_table: Optional[torch.Tensor], num_pages: int,
+                      k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], write_cache: bool,
+                      status: torch.Tensor) -> None:
+    """The general form of ``qk_norm_rope_append`` (csrc/rope_append.cu): either layout of rotated pairs, values of
+    their own size that may be divided by their root mean square and rotated by their position on the way to the
+    cache.  ``qkv`` rows: q heads | k heads | v heads."""
+    _need(qkv.stride(-1) == 1, "qkv_rotate_append: rows of qkv must be contiguous")
+    for t in (cos, sin, v_cos, v_sin, q_norm_w, k_norm_w):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous()), "qkv_rotate_append: float32 tables and weights")
+    check(library().pe_qkv_rotate_append(
+        dtype_tag(qkv.dtype), _ptr(qkv), qkv.stride(0), n_tokens, n_heads, n_kv_heads, head_dim, v_dim,
+        _ptr(q_norm_w), _ptr(k_norm_w), float(eps), _ptr(cos), _ptr(sin), rotary_dim if cos is not None else 0,
+        0 if cos is None else cos.shape[0], 1 if interleaved else 0, 1 if v_unit_norm else 0, _ptr(v_cos), _ptr(v_sin),
+        v_rotary_dim if v_cos is not None else 0, 0 if v_cos is None else v_cos.shape[0], 1 if v_interleaved else 0,
+        _ptr(token_seq), _ptr(token_pos), _ptr(seq_slot), _ptr(seq_qstart), _ptr(page_table),
+        0 if page_table is None else page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages),
+        1 if write_cache else 0, _ptr(status), _stream()), "qkv_rotate_append")
+    _count(1)
+
+
+def rmsnorm_add(stream: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float,
+                cast: Optional[torch.Tensor] = None) -> None:
+    """``stream += delta / rms(delta) * weight`` (float32 stream, in place); ``cast``, if given, gets the new
+    stream rows in the run dtype."""
+    _need(stream.dtype == torch.float32 and weight.dtype == torch.float32, "rmsnorm_add: stream and weight float32")
+    _need(stream.is_contiguous() and delta.is_contiguous() and delta.shape == stream.shape, "rmsnorm_add: shapes")
+    if cast is not None:
+        _need(cast.dtype == delta.dtype and cast.is_contiguous() and cast.shape == stream.shape, "rmsnorm_add: cast rows")
+    n, dim = stream.shape
+    check(library().pe_rmsnorm_add(dtype_tag(delta.dtype), _ptr(stream), _ptr(delta), _ptr(weight), _ptr(cast), n, dim,
+                                   float(eps), _stream()), "rmsnorm_add")
+    _count(1)
+
+
+def token_gate(gx: torch.Tensor, table: torch.Tensor, col0: int, tokens: torch.Tensor, out: torch.Tensor,
+               status: torch.Tensor) -> None:
+    """``out[t] = gelu_tanh(gx[t]) * table[tokens[t], col0 : col0 + dim]``."""
+    _need(gx.is_contiguous() and out.is_contiguous() and table.stride(1) == 1 and gx.shape == out.shape
+          and gx.dtype == out.dtype == table.dtype and tokens.dtype == torch.int32, "token_gate: shapes and dtypes")
+    n, dim = gx.shape
+    check(library().pe_token_gate(dtype_tag(gx.dtype), _ptr(gx), _ptr(table), table.stride(0), int(col0), _ptr(tokens),
+                                  _ptr(out), n, dim, table.shape[0], _ptr(status), _stream()), "token_gate")
+    _count(1)
+
+
+def token_shift_mix(x: torch.Tensor, mu: torch.Tensor, prev_state: torch.Tensor, token_seq: torch.Tensor,
+                    seq_slot: torch.Tensor, seq_qstart: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """``out[s, t] = x[t] + (x[t-1] - x[t]) * mu[s]``; a sequence's first token of the step takes
+    ``prev_state[slot]`` (float32) for ``x[t-1]``."""
+    n, width = x.shape
+    _need(x.is_contiguous() and out.is_contiguous() and mu.dtype == torch.float32 and mu.is_contiguous()
+          and mu.shape[1] == width and tuple(out.shape) == (mu.shape[0], n, width) and out.dtype == x.dtype
+          and prev_state.dtype == torch.float32 and prev_state.is_contiguous() and prev_state.shape[1] == width,
+          "token_shift_mix: shapes and dtypes")
+    check(library().pe_token_shift_mix(dtype_tag(x.dtype), _ptr(x), _ptr(mu), mu.shape[0], _ptr(prev_state),
+                                       _ptr(token_seq), _ptr(seq_slot), _ptr(seq_qstart), _ptr(out), n, width,
+                                       prev_state.shape[0], _ptr(status), _stream()), "token_shift_mix")
+    _count(1)
+
+
+def tanh_(y: torch.Tensor) -> None:
+    _need(y.is_contiguous(), "tanh_: contiguous")
+    check(library().pe_tanh_inplace(dtype_tag(y.dtype), _ptr(y), y.numel(), _stream()), "tanh_")
+    _count(1)
+
+
+def wkv_scratch_floats(n_seqs: int, heads: int, d: int, max_chunks: int) -> int:
+    return int(library().pe_wkv_scratch_floats(n_seqs, heads, d, max_chunks))
+
+
+def wkv_recurrence(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, wlin: torch.Tensor,
+                   w0: torch.Tensor, u: torch.Tensor, gnorm: torch.Tensor, eps: float, out: torch.Tensor,
+                   state: torch.Tensor, prev_state: torch.Tensor, x: torch.Tensor, seq_slot: torch.Tensor,
+                   seq_qstart: torch.Tensor, n_seqs: int, max_q: int, heads: int, d: int, chunk: int = 0,
+                   max_chunks: int = 1, scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
+    """The recurrence of csrc/wkv.cu over each sequence's tokens of this step, from and to ``state [slots, heads, d,
+    d]`` (float32); also leaves each sequence's last row of ``x`` in ``prev_state``.  ``r, k, v, g`` are views with
+    one row stride; ``chunk`` > 0 cuts prompts into chunks that run side by side (``scratch``:
+    ``wkv_scratch_floats``)."""
+    ld = r.stride(0)
+    _need(all(t.stride(-1) == 1 and t.stride(0) == ld and t.dtype == r.dtype for t in (r, k, v, g)),
+          "wkv_recurrence: r, k, v, g share dtype and row stride")
+    _need(wlin.dtype == torch.float32 and wlin.is_contiguous() and out.is_contiguous() and out.dtype == r.dtype
+          and x.dtype == r.dtype and x.is_contiguous(), "wkv_recurrence: wlin float32, out and x in the run dtype")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, d, d)
+          and prev_state.dtype == torch.float32 and prev_state.is_contiguous(), "wkv_recurrence: state tensors")
+    for t in (w0, u, gnorm):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == heads * d, "wkv_recurrence: per-channel constants")
+    launches = 3 if chunk > 0 else 1
+    check(library().pe_wkv_recurrence(
+        dtype_tag(r.dtype), _ptr(r), _ptr(k), _ptr(v), _ptr(g), ld, _ptr(wlin), _ptr(w0), _ptr(u), _ptr(gnorm),
+        float(eps), _ptr(out), _ptr(state), _ptr(prev_state), _ptr(x), x.shape[1], _ptr(seq_slot), _ptr(seq_qstart),
+        n_seqs, max_q, heads, d, state.shape[0], int(chunk), int(max_chunks), _ptr(scratch), _ptr(status), _stream()),
+        "wkv_recurrence")
+    _count(launches)
+
+
 def attention_mma_supported(dtype: torch.dtype, head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
     """Whether the tensor-core attention kernels (csrc/attention_mma.cu) take this shape."""
     return dtype == torch.bfloat16 and bool(library().pe_attention_mma_supported(head_dim, n_heads, n_kv_heads))
@@ -171,7 +300,8 @@ def attention_mma(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: int,
 def gemm_smallm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
     """Whether csrc/gemm_smallm.cu takes ``x [M, K] @ weight [N, K]^T``: bfloat16, M <= 16, K % 8 == 0."""
     return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] <= 16
-            and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.is_contiguous())
+            and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.is_contiguous()
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
 def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, pair_offset: int = 0) -> None:

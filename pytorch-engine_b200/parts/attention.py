@@ -28,18 +28,27 @@ class GQAttention:
     """params: ``hidden``, ``n_heads``, ``n_kv_heads``, ``head_dim``, ``qk_norm`` (bool), ``eps``,
     ``scale`` (None: 1/sqrt(head_dim)), ``window`` (None: all keys), ``position`` (name of a position
     encoding of the plan, or None).  weights: ``q_proj, k_proj, v_proj, o_proj`` and, with qk_norm,
-    ``q_norm, k_norm``."""
+    ``q_norm, k_norm``.
+
+    Further params, all optional: ``v_head_dim`` (values and head outputs of a size of their own), ``sink`` (true:
+    one is added to the softmax's denominator, a key of score 0 that carries no value), ``v_norm`` ("unit": each
+    head's value is divided by its root mean square, eps inside the root, no weight; it is cached so),
+    ``value_position`` (name of a rotary encoding of the plan over the value's features: the value of position j is
+    cached turned by j, and each head's output at position i is turned back by i before the output projection).
+    A rotary ``position`` may use either layout of pairs.  With any of these the mixer runs on the general kernels
+    (``qkv_rotate_append``, ``attention_generic_ex``) unless a tensor-core kernel takes the case."""
 
     graph_safe = True  # launches only; nothing in forward() waits for the device
 
     @classmethod
     def weight_decls(cls, params) -> Dict[str, WeightDecl]:
         h, nh, nkv, d = (int(params[k]) for k in ("hidden", "n_heads", "n_kv_heads", "head_dim"))
+        dv = int(params.get("v_head_dim") or d)
         decls = {
             "q_proj": WeightDecl((nh * d, h)),
             "k_proj": WeightDecl((nkv * d, h)),
-            "v_proj": WeightDecl((nkv * d, h)),
-            "o_proj": WeightDecl((h, nh * d)),
+            "v_proj": WeightDecl((nkv * dv, h)),
+            "o_proj": WeightDecl((h, nh * dv)),
         }
         if params.get("qk_norm", False):
             decls["q_norm"] = WeightDecl((d,), "norm")
@@ -48,8 +57,10 @@ class GQAttention:
 
     @classmethod
     def cache_request(cls, params) -> Optional[CacheRequest]:
-        return CacheRequest(kind="kv", kv_heads=int(params["n_kv_heads"]), head_dim=int(params["head_dim"]),
-                            window=params.get("window"))
+        d = int(params["head_dim"])
+        dv = int(params.get("v_head_dim") or d)
+        return CacheRequest(kind="kv", kv_heads=int(params["n_kv_heads"]), head_dim=d, window=params.get("window"),
+                            v_head_dim=None if dv == d else dv)
 
     def __init__(self, params, weights, runtime, positions=None) -> None:
         self.runtime = runtime
@@ -59,8 +70,13 @@ class GQAttention:
         self.head_dim = int(params["head_dim"])
         if self.n_heads % self.n_kv_heads:
             raise ValueError("n_heads must be a multiple of n_kv_heads")
-        if self.head_dim > 512:
-            raise ValueError(f"head_dim {self.head_dim} is beyond what the attention kernels take (<= 512)")
+        self.v_dim = int(params.get("v_head_dim") or self.head_dim)
+        if self.head_dim > 512 or self.v_dim > 512:
+            raise ValueError(f"head_dim {self.head_dim} / v_head_dim {self.v_dim} is beyond what the attention kernels take (<= 512)")
+        self.sink = bool(params.get("sink", False))
+        self.v_norm = params.get("v_norm")
+        if self.v_norm not in (None, "unit"):
+            raise ValueError(f"v_norm {self.v_norm!r} is not built (None or 'unit')")
         self.eps = float(params.get("eps", 1e-6))
         scale = params.get("scale")
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
@@ -81,14 +97,28 @@ class GQAttention:
             self.fused_position = bool(getattr(self.position, "fusable_rotary", False))
             if not self.fused_position and not hasattr(self.position, "apply"):
                 raise ValueError(f"position encoding {name!r} offers neither tables() nor apply(q, k, positions)")
-        self.qkv_dim = (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
+        self.value_position = None
+        vname = params.get("value_position")
+        if vname is not None:
+            self.value_position = (positions or {})[vname]
+            if not getattr(self.value_position, "fusable_rotary", False):
+                raise ValueError(f"value_position {vname!r} must be a rotary encoding with tables()")
+            if self.value_position.tables()[2] > self.v_dim:
+                raise ValueError(f"value_position {vname!r} rotates more features than a value has ({self.v_dim})")
+        interleaved = self.fused_position and getattr(self.position, "interleaved", False)
+        # what the kernels of the plain softmax attention do not do
+        self.general = bool(self.sink or self.v_norm or self.value_position is not None or self.v_dim != self.head_dim
+                            or interleaved)
+        if self.general and self.position is not None and not self.fused_position:
+            raise ValueError("the general attention path takes a rotary position encoding with tables(), or none")
+        self.qkv_dim = (self.n_heads + self.n_kv_heads) * self.head_dim + self.n_kv_heads * self.v_dim
         # tensor-core kernels where they take the shape (bfloat16, head size 64 or 128, group <= 16);
         # the generic float32-arithmetic kernels otherwise
-        self.use_mma = runtime.is_cuda and ops.attention_mma_supported(runtime.dtype, self.head_dim, self.n_heads,
-                                                                       self.n_kv_heads)
+        self.use_mma = (not self.general and runtime.is_cuda
+                        and ops.attention_mma_supported(runtime.dtype, self.head_dim, self.n_heads, self.n_kv_heads))
         # prefill on tcgen05 where that kernel takes the shape (bfloat16, head size 128, groups up to 32)
-        self.use_umma_prefill = runtime.is_cuda and ops.attention_umma_supported(runtime.dtype, self.head_dim,
-                                                                                  self.n_heads, self.n_kv_heads)
+        self.use_umma_prefill = (not self.general and runtime.is_cuda
+                                 and ops.attention_umma_supported(runtime.dtype, self.head_dim, self.n_heads, self.n_kv_heads))
 
     def forward(self, x: torch.Tensor, ctx, view, writes_cache: bool = True) -> torch.Tensor:
         rt = self.runtime
@@ -96,6 +126,14 @@ class GQAttention:
         qkv = ctx.buffer("attn.qkv", (n, self.qkv_dim), rt.dtype)
         where = (ctx.token_seq, ctx.token_pos, ctx.seq_slot, ctx.seq_qstart, view.page_table, view.num_pages,
                  view.k_pages, view.v_pages)
+        if self.general:
+            rt.linear(x, self.qkv, out=qkv)
+            self.rotate_append_general(qkv, n, ctx, view, writes_cache)
+            out = ctx.buffer("attn.out", (n, self.n_heads * self.v_dim), rt.dtype)
+            self.attend_general(qkv, out, ctx, view)
+            delta = ctx.buffer("attn.delta", (n, self.hidden), rt.dtype)
+            rt.linear(out, self.o_proj, out=delta)
+            return delta
         if self.fuses_rope_into_product(x, rt):
             # many rows: q/k-norm, rotation and the cache append ride in the epilogue of the q|k|v product (its
             # 256-column tiles are two whole heads), so q|k|v is never written and read again in between
@@ -113,6 +151,43 @@ class GQAttention:
         delta = ctx.buffer("attn.delta", (n, self.hidden), rt.dtype)
         rt.linear(out, self.o_proj, out=delta)
         return delta
+
+    # ---- the general path ---------------------------------------------------------------------------------
+    def rotate_append_general(self, qkv: torch.Tensor, n: int, ctx, view, writes_cache: bool) -> None:
+        """q/k-norm, rotation of q and k, the values' norm and rotation, and the append, in one kernel."""
+        cos = sin = vcos = vsin = None
+        rot = vrot = 0
+        inter = vinter = False
+        if self.position is not None:
+            cos, sin, rot = self.position.tables()
+            inter = bool(getattr(self.position, "interleaved", False))
+        if self.value_position is not None:
+            vcos, vsin, vrot = self.value_position.tables()
+            vinter = bool(getattr(self.value_position, "interleaved", False))
+        ops.qkv_rotate_append(qkv, n, self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim, self.q_norm, self.k_norm,
+                              self.eps, cos, sin, rot, inter, self.v_norm == "unit", vcos, vsin, vrot, vinter,
+                              ctx.token_seq, ctx.token_pos, ctx.seq_slot, ctx.seq_qstart, view.page_table, view.num_pages,
+                              view.k_pages, view.v_pages, writes_cache, self.runtime.status)
+
+    def attend_general(self, q: torch.Tensor, out: torch.Tensor, ctx, view) -> None:
+        vcos = vsin = None
+        vrot = 0
+        vinter = False
+        if self.value_position is not None:
+            vcos, vsin, vrot = self.value_position.tables()
+            vinter = bool(getattr(self.value_position, "interleaved", False))
+        scratch = None
+        max_splits = 0
+        if ctx.decode:
+            max_splits = ctx.max_splits(SPLIT_KEYS)
+            scratch = ctx.buffer(
+                "attn.scratch",
+                (ops.attention_generic_scratch_floats(ctx.n_seqs, self.n_heads, self.v_dim, max_splits),), torch.float32)
+        ops.attention_generic_ex(
+            ctx.decode, q, out, ctx.n_seqs, ctx.max_q, self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim,
+            self.scale, self.window, self.sink, vcos, vsin, vrot, vinter, ctx.seq_qstart, ctx.seq_past, ctx.seq_slot,
+            view.page_table, view.num_pages, view.k_pages, view.v_pages, scratch, SPLIT_KEYS, max_splits,
+            self.runtime.status)
 
     def fuses_rope_into_product(self, x: torch.Tensor, rt) -> bool:
         """Whether this step's q|k|v product takes norm, rotation and append into its epilogue: the many-row tcgen05

@@ -36,3 +36,45 @@ class PreNormBlock:
             mixed = self.mixer.forward(normed, ctx, view, writes_cache=False)
         self.ffn_norm.add_forward(stream, mixed, normed)
         return self.ffn.forward(normed, ctx)
+
+
+@register("arrangement", "post_norm")
+class PostNormBlock:
+    """Norm on what a sublayer returns, not on what it reads: ``x += norm1(mixer(x))``; ``x += norm2(ffn(x))`` if the
+    block has a feed-forward; ``x += side_norm(side(x))`` if it has a token side input.  Parts by name:
+    ``mixer_norm, mixer`` and optionally ``ffn_norm, ffn`` and ``side_norm, side``.  The sublayers read the stream
+    itself: in a float32 run directly, otherwise through a copy in the run dtype that every add leaves behind."""
+
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
+    def __init__(self, spec, parts, runtime) -> None:
+        self.runtime = runtime
+        self.name = spec.name
+        self.steps = [(parts["mixer"], parts["mixer_norm"], True)]
+        if "ffn" in parts:
+            self.steps.append((parts["ffn"], parts["ffn_norm"], False))
+        if "side" in parts:
+            self.steps.append((parts["side"], parts["side_norm"], False))
+
+    def forward(self, stream: torch.Tensor, pending: Optional[torch.Tensor], ctx, view, writes_cache: bool = True):
+        rt = self.runtime
+        if pending is not None:       # a block before this one left its last delta to be added
+            stream.add_(pending)
+            ctx.stream_copy = None
+        same = rt.dtype == torch.float32
+        x = stream
+        if not same:
+            x = getattr(ctx, "stream_copy", None)
+            if x is None:
+                x = ctx.buffer("block.x", tuple(stream.shape), rt.dtype)
+                x.copy_(stream)
+        cast = None if same else ctx.buffer("block.x", tuple(stream.shape), rt.dtype)
+        for part, norm, is_mixer in self.steps:
+            if is_mixer:
+                delta = part.forward(x, ctx, view) if writes_cache else part.forward(x, ctx, view, writes_cache=False)
+            else:
+                delta = part.forward(x, ctx)
+            norm.add_after(stream, delta, cast)
+            x = stream if same else cast
+        ctx.stream_copy = None if same else cast
+        return None

@@ -36,7 +36,7 @@ class TokenEmbedding:
 class LinearHead:
     """params: ``vocab``, ``hidden``.  weights: ``weight [vocab, hidden]``; a tied head names the
     embedding's tensor and shares its storage (pygguf_engine/model.py:1678-1683, 2206-2214).
-    Output: float32 logits."""
+    ``scale`` (optional): a factor on the logits.  Output: float32 logits."""
 
     graph_safe = True  # launches only; nothing in forward() waits for the device
 
@@ -48,6 +48,10 @@ class LinearHead:
         self.runtime = runtime
         self.vocab = int(params["vocab"])
         self.weight = runtime.adopt(weights["weight"])
+        self.scale = float(params.get("scale", 1.0) or 1.0)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.runtime.linear(x, self.weight, out_dtype=torch.float32)
+        logits = self.runtime.linear(x, self.weight, out_dtype=torch.float32)
+        if self.scale != 1.0:
+            logits.mul_(self.scale)
+        return logits

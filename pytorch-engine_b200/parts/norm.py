@@ -36,3 +36,7 @@ class RMSNorm:
         out = torch.empty_like(x) if out is None else out
         ops.rmsnorm(x, self.weight, out, self.eps)
         return out
+
+    def add_after(self, stream: torch.Tensor, delta: torch.Tensor, cast: Optional[torch.Tensor] = None) -> None:
+        """The norm on what is added: ``stream += rmsnorm(delta) * w``; ``cast`` gets the new rows in the run dtype."""
+        ops.rmsnorm_add(stream, delta, self.weight, self.eps, cast)

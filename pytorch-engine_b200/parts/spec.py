@@ -103,18 +103,28 @@ class ModelPlan:
 class WeightDecl:
     """What a part expects of one of its weights: shape, and the ``role`` that decides how a
     random model fills it and what the part converts it to (``matrix``/``embedding``: normal
-    with the given std, run dtype; ``norm``: one plus normal, float32; ``table_int``: int32)."""
+    with the given std, run dtype; ``norm``: one plus normal, float32; ``table_int``: int32;
+    ``unit``: uniform in (0, 1), a mixing coefficient).  ``any_dims`` lists the dimensions whose size the
+    checkpoint decides (a projection's rank that no configuration key names): the loader accepts any size
+    there, ``shape`` holds the size that random weights get, and the part reads the tensor's own shape."""
 
     shape: Tuple[int, ...]
     role: str = "matrix"
+    any_dims: Tuple[int, ...] = ()
+
+    def fits(self, got) -> bool:
+        got = tuple(got)
+        return len(got) == len(self.shape) and all(
+            i in self.any_dims or int(g) == int(w) for i, (g, w) in enumerate(zip(got, self.shape)))
 
 
 @dataclass(frozen=True)
 class CacheRequest:
     """What a mixer needs the cache to hold per sequence.
 
-    ``kind`` "kv": keys and values of every position, ``kv_heads x head_dim`` each, and with
-    ``window`` only the last ``window`` positions need to stay.  ``kind`` "state": tensors of fixed
+    ``kind`` "kv": keys and values of every position, ``kv_heads x head_dim`` each (values
+    ``kv_heads x v_head_dim`` when that is given and differs), and with ``window`` only the last
+    ``window`` positions need to stay.  ``kind`` "state": tensors of fixed
     shape per sequence (``state_shapes``: name -> (shape, torch dtype name)), zero when a
     sequence starts.  Entries with equal requests share one group of storage.
     """
@@ -124,6 +134,11 @@ class CacheRequest:
     head_dim: int = 0
     window: Optional[int] = None
     state_shapes: Tuple[Tuple[str, Tuple[int, ...], str], ...] = ()
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
     def group_key(self):
-        return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shapes)
+        return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shapes, self.value_dim)

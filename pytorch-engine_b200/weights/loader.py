@@ -69,7 +69,7 @@ def expected_tensors(plan: ModelPlan) -> Dict[str, WeightDecl]:
             if local not in spec.weights:
                 raise KeyError(f"{label}: the plan gives no checkpoint name for weight {local!r} of kind {spec.kind!r}")
             name = spec.weights[local]
-            if name in out and tuple(out[name].shape) != tuple(decl.shape):
+            if name in out and (tuple(out[name].shape) != tuple(decl.shape) or out[name].any_dims != decl.any_dims):
                 raise ValueError(f"tensor {name!r} is used with two shapes: {out[name].shape} and {decl.shape}")
             out.setdefault(name, decl)
     return out
@@ -132,7 +132,7 @@ def load_weights(folder: str, plan: ModelPlan, device="cpu", dtype: Optional[tor
     check_equal = sorted(n for n in extra if n in duplicates and duplicates[n] in want)
     unexpected = sorted(n for n in extra if n not in check_equal and not any(fnmatch.fnmatchcase(n, pat) for pat in ignored))
     wrong = sorted((n, where[n][1], tuple(want[n].shape)) for n in want
-                   if n in where and tuple(where[n][1]) != tuple(want[n].shape))
+                   if n in where and not want[n].fits(where[n][1]))
     bad_dtype = sorted((n, where[n][2], want[n].role, " / ".join(usable_tags(want[n].role))) for n in want
                        if n in where and where[n][2] not in usable_tags(want[n].role))
     conflicting = []

@@ -47,7 +47,9 @@ def random_weights(plan: ModelPlan, seed: int, device="cpu", norm_dtype: torch.d
             out[name] = t
             continue
         x = torch.randn(decl.shape, generator=gen, device=device, dtype=torch.float32) * WEIGHT_STD
-        if decl.role == "norm":
+        if decl.role == "unit":
+            out[name] = torch.rand(decl.shape, generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+        elif decl.role == "norm":
             out[name] = (1.0 + x).to(torch.bfloat16).to(norm_dtype)
         else:
             out[name] = x.to(torch.bfloat16)
