@@ -86,13 +86,18 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens that live requests hold at any time, each request rounded up to 64")
+                    help="most tokens that live requests hold at any time")
     args = ap.parse_args(argv)
     from ..cache import PAGE_TOKENS, pages_for
     from ..config.registry import load_config
 
     cfg = load_config(args.model)
-    cache_tokens = pages_for(max(args.max_tokens, 1)) * PAGE_TOKENS
-    engine = Engine(args.model, dtype=args.dtype, max_context_len=min(cfg.max_positions, cache_tokens),
-                    max_cache_tokens=cache_tokens, max_slots=min(pages_for(cache_tokens), 8192))
+    # ``--max-tokens`` counts tokens, the cache hands out pages: every live request may leave most of its last page
+    # empty, and there can be as many live requests as tokens.  So: the pages that the tokens fill, and one more page
+    # and one slot for each of up to 1,024 requests.
+    n = max(args.max_tokens, 1)
+    requests = min(n, 1024)
+    cache_tokens = (pages_for(n) + requests) * PAGE_TOKENS
+    engine = Engine(args.model, dtype=args.dtype, max_context_len=min(cfg.max_positions, pages_for(n) * PAGE_TOKENS),
+                    max_cache_tokens=cache_tokens, max_slots=requests)
     return TraceReplayer(engine, args.out).run(sys.stdin)

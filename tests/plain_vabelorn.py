@@ -25,6 +25,29 @@ from typing import Dict, List, Optional
 import torch
 
 
+# ``STORE``: None, or a 16-bit dtype in which the results of matrix products and what a cache keeps are rounded (and
+# brought back), at about the places where an engine that runs in that dtype rounds.  It shows how far rounding alone
+# moves the logits of a model: the measure against which a 16-bit run can be judged.  ``with stored(torch.bfloat16): ..``
+STORE = None
+
+
+class stored:
+    def __init__(self, dtype):
+        self.dtype = dtype
+
+    def __enter__(self):
+        global STORE
+        self.before, STORE = STORE, self.dtype
+
+    def __exit__(self, *exc):
+        global STORE
+        STORE = self.before
+
+
+def st(x: torch.Tensor) -> torch.Tensor:
+    return x if STORE is None else x.to(STORE).to(x.dtype)
+
+
 def rms(x: torch.Tensor, eps: float) -> torch.Tensor:
     return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
 
@@ -81,9 +104,9 @@ def attention_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict
     rot = m["rot"]
     dims = int(rot["dims"])
     pos = torch.arange(T, dtype=h.dtype) if positions is None else positions.to(h.dtype)
-    q = (h @ W[p + "q"].T).view(T, H, d)
-    k = (h @ W[p + "k"].T).view(T, G, d)
-    v = (h @ W[p + "v"].T).view(T, G, dv)
+    q = st(h @ W[p + "q"].T).view(T, H, d)
+    k = st(h @ W[p + "k"].T).view(T, G, d)
+    v = st(h @ W[p + "v"].T).view(T, G, dv)
     q = rms(q, eps) * W[p + "q.norm"]
     k = rms(k, eps) * W[p + "k.norm"]
     f, mult = key_frequencies(rot, h.dtype)
@@ -92,7 +115,8 @@ def attention_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict
     k = torch.cat([rotate_interleaved(k[..., :dims].transpose(0, 1), ang, mult).transpose(0, 1), k[..., dims:]], dim=-1)
     v = rms(v, eps)
     vang = pos[:, None] * value_frequencies(rot, dv, h.dtype)[None, :]
-    v = rotate_interleaved(v.transpose(0, 1), vang).transpose(0, 1)            # [T, G, dv]
+    v = st(rotate_interleaved(v.transpose(0, 1), vang).transpose(0, 1))        # [T, G, dv]
+    q, k = st(q), st(k)
     out = torch.empty(T, H, dv, dtype=h.dtype)
     causal = pos[None, :] <= pos[:, None]
     for head in range(H):
@@ -103,11 +127,11 @@ def attention_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict
         pr = e / (1.0 + e.sum(dim=-1, keepdim=True))
         out[:, head] = pr @ v[:, g]
     out = rotate_interleaved(out.transpose(0, 1), -vang).transpose(0, 1)
-    return out.reshape(T, H * dv) @ W[p + "o"].T
+    return st(st(out.reshape(T, H * dv)) @ W[p + "o"].T)
 
 
 def wkv_decay(mix_w: torch.Tensor, W: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
-    return torch.exp(-torch.exp(torch.tanh(mix_w @ W[p + "w1"].T) @ W[p + "w2"].T + W[p + "w0"]))
+    return torch.exp(-torch.exp(st(torch.tanh(st(mix_w @ W[p + "w1"].T))) @ W[p + "w2"].T + W[p + "w0"]))
 
 
 def wkv_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float,
@@ -118,11 +142,11 @@ def wkv_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict, eps:
     prev0 = torch.zeros(width, dtype=h.dtype) if state is None else state["prev"]
     S = torch.zeros(H, d, d, dtype=h.dtype) if state is None else state["S"].clone()
     hp = torch.cat([prev0[None], h[:-1]], dim=0)
-    mix = {s: h + (hp - h) * W[p + "mu." + s] for s in "rkvgw"}
-    r = (mix["r"] @ W[p + "r"].T).view(T, H, d)
-    k = (mix["k"] @ W[p + "k"].T).view(T, H, d)
-    v = (mix["v"] @ W[p + "v"].T).view(T, H, d)
-    gate = silu(mix["g"] @ W[p + "g"].T)
+    mix = {s: st(h + (hp - h) * W[p + "mu." + s]) for s in "rkvgw"}
+    r = st(mix["r"] @ W[p + "r"].T).view(T, H, d)
+    k = st(mix["k"] @ W[p + "k"].T).view(T, H, d)
+    v = st(mix["v"] @ W[p + "v"].T).view(T, H, d)
+    gate = silu(st(mix["g"] @ W[p + "g"].T))
     w = wkv_decay(mix["w"], W, p).view(T, H, d)
     u = W[p + "u"].to(h.dtype)
     o = torch.empty(T, H, d, dtype=h.dtype)
@@ -132,18 +156,18 @@ def wkv_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict, eps:
         S = w[t, :, :, None] * S + kv
     if state is not None:
         state["prev"], state["S"] = h[-1].clone(), S
-    o = rms(o, eps).reshape(T, H * d) * W[p + "norm"] * gate
-    return o @ W[p + "o"].T
+    o = st(rms(o, eps).reshape(T, H * d) * W[p + "norm"] * gate)
+    return st(o @ W[p + "o"].T)
 
 
 def dense_ff(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
-    return (silu(h @ W[p + "gate"].T) * (h @ W[p + "up"].T)) @ W[p + "down"].T
+    return st(st(silu(h @ W[p + "gate"].T) * (h @ W[p + "up"].T)) @ W[p + "down"].T)
 
 
 def side_input(x: torch.Tensor, tokens: torch.Tensor, W: Dict[str, torch.Tensor], layer: int, ds: int, eps: float) -> torch.Tensor:
     p = f"l{layer}.side."
     e = W["side.embed"][tokens][:, layer * ds:(layer + 1) * ds]
-    y = (gelu_tanh(x @ W[p + "gate"].T) * e) @ W[p + "proj"].T
+    y = st(st(gelu_tanh(st(x @ W[p + "gate"].T)) * e) @ W[p + "proj"].T)
     return rms(y, eps) * W[p + "norm"]
 
 
@@ -166,24 +190,24 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
         p = f"l{i}.mix."
         if layer["type"] == "attention":
             if state is None:
-                mixed = attention_mixer(x, W, p, layer["mixer"], eps)
+                mixed = attention_mixer(st(x), W, p, layer["mixer"], eps)
             else:
                 # the plain way to continue: keep the mixer's inputs of all earlier tokens and run over all of them
-                st = state[i]
-                st["h"] = x if st.get("h") is None else torch.cat([st["h"], x], dim=0)
-                mixed = attention_mixer(st["h"], W, p, layer["mixer"], eps)[-T:]
+                kept = state[i]
+                kept["h"] = st(x) if kept.get("h") is None else torch.cat([kept["h"], st(x)], dim=0)
+                mixed = attention_mixer(kept["h"], W, p, layer["mixer"], eps)[-T:]
         elif layer["type"] == "wkv":
-            mixed = wkv_mixer(x, W, p, layer["mixer"], eps, None if state is None else state[i])
+            mixed = wkv_mixer(st(x), W, p, layer["mixer"], eps, None if state is None else state[i])
         else:
             raise ValueError(layer["type"])
         x = x + rms(mixed, eps) * W[f"l{i}.norm1"]
         if layer.get("mlp"):
-            x = x + rms(dense_ff(x, W, f"l{i}.mlp."), eps) * W[f"l{i}.norm2"]
+            x = x + rms(dense_ff(st(x), W, f"l{i}.mlp."), eps) * W[f"l{i}.norm2"]
         if ds:
-            x = x + side_input(x, tok, W, i, ds, eps)
+            x = x + side_input(st(x), tok, W, i, ds, eps)
         if layers_out is not None:
             layers_out.append(x.clone())
-    return (rms(x, eps) * W["final.norm"]) @ W["embed"].T * float(cfg["logit_scale"])
+    return st(rms(x, eps) * W["final.norm"]) @ W["embed"].T * float(cfg.get("logit_scale", 1.0))
 
 
 def new_state(cfg: dict, dtype=torch.float64) -> list:
