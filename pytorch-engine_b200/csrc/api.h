@@ -37,6 +37,11 @@ int pe_attention_mma(int decode, const void* q, long long q_ld, void* out, long 
     const int* seq_slot, const int* page_table, int table_stride, int num_pages, const void* k_pages,
     const void* v_pages, float* scratch, int split_keys, int max_splits, int min_range_keys, int* status,
     cudaStream_t stream);
+int pe_attention_mma_ex(int decode, const void* q, long long q_ld, void* out, long long out_ld, int n_seqs, int max_q,
+    int n_heads, int n_kv_heads, int head_dim, float scale, int window, int sink, const float* out_cos,
+    const float* out_sin, int out_rows, const int* seq_qstart, const int* seq_past, const int* seq_slot,
+    const int* page_table, int table_stride, int num_pages, const void* k_pages, const void* v_pages, float* scratch,
+    int split_keys, int max_splits, int min_range_keys, int* status, cudaStream_t stream);
 
 // attention_umma.cu
 int pe_attention_umma_supported(int head_dim, int n_heads, int n_kv_heads);
@@ -44,6 +49,11 @@ int pe_attention_umma_prefill(const void* q, long long q_ld, long long n_tokens,
     int n_seqs, int max_q, int n_heads, int n_kv_heads, int head_dim, float scale, int window, const int* seq_qstart,
     const int* seq_past, const int* seq_slot, const int* page_table, int table_stride, int num_pages,
     const void* k_pages, const void* v_pages, int n_sms, int* work_counter, int* status, cudaStream_t stream);
+int pe_attention_umma_prefill_ex(const void* q, long long q_ld, long long n_tokens, void* out, long long out_ld,
+    int n_seqs, int max_q, int n_heads, int n_kv_heads, int head_dim, float scale, int window, int sink,
+    const float* out_cos, const float* out_sin, int out_rows, const int* seq_qstart, const int* seq_past,
+    const int* seq_slot, const int* page_table, int table_stride, int num_pages, const void* k_pages,
+    const void* v_pages, int n_sms, int* work_counter, int* status, cudaStream_t stream);
 
 // embedding.cu
 int pe_embed_gather(int dtype, const void* table, const int* ids, float* out, int n_tokens, int hidden, int vocab,

@@ -44,6 +44,10 @@ struct Args {
   const __nv_bfloat16* k_pages; const __nv_bfloat16* v_pages;
   int* status;
   float* part_acc; float* part_lse; int split_keys, max_splits, min_range_keys;
+  // a sink in the softmax (one added to its denominator) and each head's output turned back by the angle of the
+  // query's position (interleaved pairs over the whole head; tables [out_rows, HD/2]); off: 0 and null
+  int sink;
+  const float* out_cos; const float* out_sin; int out_rows;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -281,6 +285,10 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
     }
     __syncthreads();  // the stage may be overwritten in the next round
   }
+  if (a.sink) {   // the sink's score is 0: its weight relative to the running maximum (in powers of two)
+    l_lo += fast_exp2(-m_lo);
+    l_hi += fast_exp2(-m_hi);
+  }
   const float inv_lo = 1.f / fmaxf(l_lo, 1e-20f), inv_hi = 1.f / fmaxf(l_hi, 1e-20f);
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
@@ -289,6 +297,23 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
     const int tok = row / group, head = kvh * group + row % group;
     __nv_bfloat16* dst = a.out + (size_t)(q0 + tok) * a.out_ld + (size_t)head * HD;
     const float inv = half ? inv_hi : inv_lo;
+    if (a.out_cos) {
+      // a thread's two adjacent features are one interleaved pair: pair n*4 + t turns back by the position's angle
+      const int pos = half ? pos_hi : pos_lo;
+      if (pos < 0 || pos >= a.out_rows) {
+        report(a.status, kStatusPositionOutOfRange, q0 + tok, pos, a.out_rows);
+        continue;
+      }
+      const float* cs = a.out_cos + (size_t)pos * (HD / 2);
+      const float* sn = a.out_sin + (size_t)pos * (HD / 2);
+#pragma unroll
+      for (int n = 0; n < NO; ++n) {
+        const float c = cs[n * 4 + t], sv = sn[n * 4 + t];
+        const float x0 = o[n][half * 2] * inv, x1 = o[n][half * 2 + 1] * inv;
+        *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) = pack_bf16(x0 * c + x1 * sv, x1 * c - x0 * sv);
+      }
+      continue;
+    }
 #pragma unroll
     for (int n = 0; n < NO; ++n) {
       const uint32_t v = pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
@@ -522,7 +547,8 @@ __global__ void decode_merge_kernel(Args a) {
   // maximum, denominator and sum, in range order.
   constexpr int G = 8;
   for (int c = threadIdx.x; c < HD; c += blockDim.x) {
-    float mx = -INFINITY, denom = 0.f, v = 0.f;
+    // with a sink the fold starts from one more range whose log-sum is 0 and whose output is 0
+    float mx = a.sink ? 0.f : -INFINITY, denom = a.sink ? 1.f : 0.f, v = 0.f;
     for (int s0 = first; s0 < n_splits; s0 += G) {
       float e[G], acc[G];
 #pragma unroll
@@ -546,7 +572,19 @@ __global__ void decode_merge_kernel(Args a) {
       }
       mx = m_new;
     }
-    o[c] = __float2bfloat16_rn(v / fmaxf(denom, 1e-20f));
+    v = v / fmaxf(denom, 1e-20f);
+    if (a.out_cos) {
+      // features c and c ^ 1 (adjacent lanes) are one interleaved pair; every lane of the warp is here (HD % 32 == 0)
+      const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+      const int pos = len - 1;
+      if (pos < 0 || pos >= a.out_rows) {
+        if (c == 0) report(a.status, kStatusPositionOutOfRange, tq, pos, a.out_rows);
+        continue;
+      }
+      const float cs = a.out_cos[(size_t)pos * (HD / 2) + (c >> 1)], sn = a.out_sin[(size_t)pos * (HD / 2) + (c >> 1)];
+      v = (c & 1) ? v * cs - other * sn : v * cs + other * sn;
+    }
+    o[c] = __float2bfloat16_rn(v);
   }
 }
 
@@ -633,7 +671,21 @@ extern "C" int pe_attention_mma(int decode, const void* q, long long q_ld, void*
                                 int table_stride, int num_pages, const void* k_pages, const void* v_pages,
                                 float* scratch, int split_keys, int max_splits, int min_range_keys, int* status,
                                 cudaStream_t stream) {
+  return pe_attention_mma_ex(decode, q, q_ld, out, out_ld, n_seqs, max_q, n_heads, n_kv_heads, head_dim, scale, window, 0,
+                             nullptr, nullptr, 0, seq_qstart, seq_past, seq_slot, page_table, table_stride, num_pages,
+                             k_pages, v_pages, scratch, split_keys, max_splits, min_range_keys, status, stream);
+}
+
+// The same with a sink in the softmax and, with tables, each head's output turned back by the query's position
+// (interleaved pairs over the whole head; out_cos, out_sin: float32 [out_rows, head_dim / 2]).
+extern "C" int pe_attention_mma_ex(int decode, const void* q, long long q_ld, void* out, long long out_ld, int n_seqs,
+                                   int max_q, int n_heads, int n_kv_heads, int head_dim, float scale, int window, int sink,
+                                   const float* out_cos, const float* out_sin, int out_rows, const int* seq_qstart,
+                                   const int* seq_past, const int* seq_slot, const int* page_table, int table_stride,
+                                   int num_pages, const void* k_pages, const void* v_pages, float* scratch,
+                                   int split_keys, int max_splits, int min_range_keys, int* status, cudaStream_t stream) {
   if (n_seqs <= 0) return PE_OK;
+  if ((out_cos == nullptr) != (out_sin == nullptr)) return PE_ERR_BAD_ARGUMENT;
   if (!pe_attention_mma_supported(head_dim, n_heads, n_kv_heads)) return PE_ERR_UNSUPPORTED_SIZE;
   // 16-byte vector loads of q rows
   if ((q_ld * 2) % 16 || ((uintptr_t)q % 16) || (out_ld * 2) % 4 || ((uintptr_t)out % 4)) return PE_ERR_BAD_ARGUMENT;
@@ -646,6 +698,7 @@ extern "C" int pe_attention_mma(int decode, const void* q, long long q_ld, void*
   a.page_table = page_table; a.table_stride = table_stride; a.num_pages = num_pages;
   a.k_pages = (const __nv_bfloat16*)k_pages; a.v_pages = (const __nv_bfloat16*)v_pages; a.status = status;
   a.part_acc = nullptr; a.part_lse = nullptr; a.split_keys = 0; a.max_splits = 0; a.min_range_keys = 0;
+  a.sink = sink; a.out_cos = out_cos; a.out_sin = out_sin; a.out_rows = out_rows;
   if (decode) {
     if (!scratch || split_keys < 0 || split_keys % pe::fa::BN || max_splits <= 0) return PE_ERR_BAD_ARGUMENT;
     if (min_range_keys < 0 || min_range_keys % pe::fa::BN) return PE_ERR_BAD_ARGUMENT;

@@ -65,6 +65,10 @@ struct Args {
   int* status;
   int tiles, n_seqs;      // row tiles of the step's longest sequence; sequences
   int* work_counter;      // [0] next rank, [1] blocks that are through; both zero between launches.  May be null.
+  // a sink in the softmax (one added to its denominator) and each head's output turned back by the angle of the
+  // query's position (interleaved pairs over the whole head; tables [out_rows, HD/2]); off: 0 and null
+  int sink;
+  const float* out_cos; const float* out_sin; int out_rows;
 };
 
 // One work item: the rows [row0, row0 + rows_blk) of sequence b's (token, head) rows for kv head kvh.
@@ -592,15 +596,37 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
       }
       if (ok && tma::mbar_wait(&o_done, it & 1)) {
         fence_after_sync();
+        // the sink's score is 0: its weight relative to the reference that the row's weights were taken against
+        if (a.sink) l += fast_exp2(-((m_ref == -INFINITY) ? 0.f : m_ref));
         const float inv = 1.f / fmaxf(l, 1e-20f);
         const int tok = row / group, head = w.kvh * group + row % group;
         __nv_bfloat16* dst = a.out + (size_t)(w.q0 + tok) * a.out_ld + (size_t)head * HD;
+        const bool turn = a.out_cos != nullptr;
+        const bool pos_ok = qpos >= 0 && qpos < a.out_rows;
+        if (turn && live && !pos_ok) report(a.status, kStatusPositionOutOfRange, w.q0 + tok, qpos, a.out_rows);
+        const float* cs = turn && pos_ok ? a.out_cos + (size_t)qpos * (HD / 2) : nullptr;
+        const float* sn = turn && pos_ok ? a.out_sin + (size_t)qpos * (HD / 2) : nullptr;
 #pragma unroll 1
         for (int c = 0; c < HD; c += 32) {
           uint32_t ov[32];
           tmem_ld32(tmem_o + c + lane_off, ov);
           tmem_ld_wait();
-          if (live) {
+          if (live && cs) {
+            // a row's adjacent features are interleaved pairs: pair (c + 2k) / 2 turns back by the position's angle
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float4 c4 = *reinterpret_cast<const float4*>(cs + c / 2 + 4 * i);
+              const float4 s4 = *reinterpret_cast<const float4*>(sn + c / 2 + 4 * i);
+              const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+              uint32_t packed[4];
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const float x0 = __uint_as_float(ov[8 * i + 2 * k]) * inv, x1 = __uint_as_float(ov[8 * i + 2 * k + 1]) * inv;
+                packed[k] = pack2(x0 * cc[k] + x1 * ss[k], x1 * cc[k] - x0 * ss[k]);
+              }
+              *reinterpret_cast<uint4*>(dst + c + 8 * i) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+          } else if (live && !turn) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint4 o4;
@@ -650,8 +676,23 @@ extern "C" int pe_attention_umma_prefill(const void* q, long long q_ld, long lon
                                          int window, const int* seq_qstart, const int* seq_past, const int* seq_slot,
                                          const int* page_table, int table_stride, int num_pages, const void* k_pages,
                                          const void* v_pages, int n_sms, int* work_counter, int* status, cudaStream_t stream) {
+  return pe_attention_umma_prefill_ex(q, q_ld, n_tokens, out, out_ld, n_seqs, max_q, n_heads, n_kv_heads, head_dim, scale,
+                                      window, 0, nullptr, nullptr, 0, seq_qstart, seq_past, seq_slot, page_table,
+                                      table_stride, num_pages, k_pages, v_pages, n_sms, work_counter, status, stream);
+}
+
+// The same with a sink in the softmax and, with tables, each head's output turned back by the query's position
+// (interleaved pairs over the whole head; out_cos, out_sin: float32 [out_rows, 64], 16-byte aligned).
+extern "C" int pe_attention_umma_prefill_ex(const void* q, long long q_ld, long long n_tokens, void* out, long long out_ld,
+                                            int n_seqs, int max_q, int n_heads, int n_kv_heads, int head_dim, float scale,
+                                            int window, int sink, const float* out_cos, const float* out_sin, int out_rows,
+                                            const int* seq_qstart, const int* seq_past, const int* seq_slot,
+                                            const int* page_table, int table_stride, int num_pages, const void* k_pages,
+                                            const void* v_pages, int n_sms, int* work_counter, int* status,
+                                            cudaStream_t stream) {
   using namespace pe::fau;
   if (n_seqs <= 0) return PE_OK;
+  if ((out_cos == nullptr) != (out_sin == nullptr) || ((uintptr_t)out_cos % 16) || ((uintptr_t)out_sin % 16)) return PE_ERR_BAD_ARGUMENT;
   if (!pe_attention_umma_supported(head_dim, n_heads, n_kv_heads)) return PE_ERR_UNSUPPORTED_SIZE;
   if (((uintptr_t)q % 16) || (q_ld * 2) % 16 || ((uintptr_t)out % 16) || (out_ld * 2) % 16) return PE_ERR_BAD_ARGUMENT;
   Args a;
@@ -659,6 +700,7 @@ extern "C" int pe_attention_umma_prefill(const void* q, long long q_ld, long lon
   a.group = n_heads / n_kv_heads; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
   a.seq_qstart = seq_qstart; a.seq_past = seq_past; a.seq_slot = seq_slot;
   a.page_table = page_table; a.table_stride = table_stride; a.num_pages = num_pages; a.status = status;
+  a.sink = sink; a.out_cos = out_cos; a.out_sin = out_sin; a.out_rows = out_rows;
   pe::tma::EncodeTiledFn fn = pe::tma::encode_fn();
   if (fn == nullptr) return -5;
   CUtensorMap qmap, kmap, vmap;

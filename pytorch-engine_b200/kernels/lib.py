@@ -70,6 +70,8 @@ _SIGNATURES = {
                              I, P, P],
     "pe_attention_generic_ex": [I, I, P, L, P, L, I, I, I, I, I, I, F, I, I, P, P, I, I, I, P, P, P, P, I, I, P, P, P,
                                 I, I, P, P],
+    "pe_attention_mma_ex": [I, P, L, P, L, I, I, I, I, I, F, I, I, P, P, I, P, P, P, P, I, I, P, P, P, I, I, I, P, P],
+    "pe_attention_umma_prefill_ex": [P, L, L, P, L, I, I, I, I, I, F, I, I, P, P, I, P, P, P, P, I, I, P, P, I, P, P, P],
     "pe_attention_decode_noalloc": [I, P, L, P, L, I, I, I, I, F, I, P, P, P, P, I, I, P, P, I, I, P, P],
 }
 _RESTYPES = {"pe_wait_limit_polls": (L, []),

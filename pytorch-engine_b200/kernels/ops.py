@@ -274,6 +274,15 @@ def wkv_recurrence(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.T
     _count(launches)
 
 
+def _check_out_tables(out_cos, out_sin, head_dim: int) -> None:
+    if out_cos is None and out_sin is None:
+        return
+    _need(out_cos is not None and out_sin is not None and out_cos.dtype == out_sin.dtype == torch.float32
+          and out_cos.is_contiguous() and out_sin.is_contiguous() and out_cos.shape == out_sin.shape
+          and out_cos.shape[1] * 2 == head_dim and out_cos.data_ptr() % 16 == 0 and out_sin.data_ptr() % 16 == 0,
+          "attention: the output's angle tables are float32 [rows, head_dim / 2], over the whole head")
+
+
 def attention_mma_supported(dtype: torch.dtype, head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
     """Whether the tensor-core attention kernels (csrc/attention_mma.cu) take this shape."""
     return dtype == torch.bfloat16 and bool(library().pe_attention_mma_supported(head_dim, n_heads, n_kv_heads))
@@ -283,15 +292,20 @@ def attention_mma(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: int,
                   n_kv_heads: int, head_dim: int, scale: float, window: int, seq_qstart: torch.Tensor,
                   seq_past: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int,
                   k_pages: torch.Tensor, v_pages: torch.Tensor, scratch: Optional[torch.Tensor], split_keys: int,
-                  max_splits: int, status: torch.Tensor, min_range_keys: int = 0) -> None:
+                  max_splits: int, status: torch.Tensor, min_range_keys: int = 0, sink: bool = False,
+                  out_cos: Optional[torch.Tensor] = None, out_sin: Optional[torch.Tensor] = None) -> None:
     """Same contract as ``attention_generic``, bfloat16 only, head sizes 64 and 128, groups up to 16.
     With ``split_keys`` 0 a sequence's keys are shared out evenly over ``max_splits`` ranges of whole pages,
-    each of at least ``min_range_keys`` keys."""
+    each of at least ``min_range_keys`` keys.  ``sink``: one added to the softmax's denominator.  ``out_cos,
+    out_sin`` (float32 ``[rows, head_dim / 2]``): each head's output is turned back by the angle of the query's
+    position, interleaved pairs over the whole head."""
     _need(q.stride(-1) == 1 and out.stride(-1) == 1, "attention: rows must be contiguous")
     _need(q.dtype == out.dtype == k_pages.dtype == torch.bfloat16, "attention_mma: bfloat16 tensors only")
-    check(library().pe_attention_mma(
+    _check_out_tables(out_cos, out_sin, head_dim)
+    check(library().pe_attention_mma_ex(
         1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), n_seqs, max_q, n_heads, n_kv_heads,
-        head_dim, float(scale), int(window), _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot), _ptr(page_table),
+        head_dim, float(scale), int(window), 1 if sink else 0, _ptr(out_cos), _ptr(out_sin),
+        0 if out_cos is None else out_cos.shape[0], _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot), _ptr(page_table),
         page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages), _ptr(scratch), split_keys, max_splits,
         int(min_range_keys), _ptr(status), _stream()), "attention_mma")
     _count(2 if decode else 1)
@@ -456,14 +470,18 @@ def _work_counter(device: torch.device) -> torch.Tensor:
 def attention_umma_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_q: int, n_heads: int, n_kv_heads: int,
                            head_dim: int, scale: float, window: int, seq_qstart: torch.Tensor, seq_past: torch.Tensor,
                            seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int, k_pages: torch.Tensor,
-                           v_pages: torch.Tensor, status: torch.Tensor) -> None:
+                           v_pages: torch.Tensor, status: torch.Tensor, sink: bool = False,
+                           out_cos: Optional[torch.Tensor] = None, out_sin: Optional[torch.Tensor] = None) -> None:
     """Prefill attention on tcgen05 (bfloat16, head size 128, groups up to 32); ``q`` holds the step's
-    query rows (the first ``n_heads * head_dim`` features of each row of the fused q|k|v buffer)."""
+    query rows (the first ``n_heads * head_dim`` features of each row of the fused q|k|v buffer).  ``sink``,
+    ``out_cos``, ``out_sin``: as for ``attention_mma``."""
     _need(q.stride(-1) == 1 and out.stride(-1) == 1, "attention: rows must be contiguous")
     _need(q.dtype == out.dtype == k_pages.dtype == torch.bfloat16, "attention_umma: bfloat16 tensors only")
-    check(library().pe_attention_umma_prefill(
+    _check_out_tables(out_cos, out_sin, head_dim)
+    check(library().pe_attention_umma_prefill_ex(
         _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), n_seqs, max_q, n_heads, n_kv_heads, head_dim,
-        float(scale), int(window), _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot), _ptr(page_table),
+        float(scale), int(window), 1 if sink else 0, _ptr(out_cos), _ptr(out_sin),
+        0 if out_cos is None else out_cos.shape[0], _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot), _ptr(page_table),
         page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages), sm_count(q.device), _ptr(_work_counter(q.device)), _ptr(status), _stream()),
         "attention_umma_prefill")
     _count(1)

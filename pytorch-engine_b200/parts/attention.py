@@ -114,11 +114,17 @@ class GQAttention:
         self.qkv_dim = (self.n_heads + self.n_kv_heads) * self.head_dim + self.n_kv_heads * self.v_dim
         # tensor-core kernels where they take the shape (bfloat16, head size 64 or 128, group <= 16);
         # the generic float32-arithmetic kernels otherwise
-        self.use_mma = (not self.general and runtime.is_cuda
+        # (with a sink or turned values too, if keys and values have one size and the values turn in interleaved pairs
+        # over the whole head: these kernels take both in their epilogues)
+        vp = self.value_position
+        fast_ok = self.v_dim == self.head_dim and (vp is None or (getattr(vp, "interleaved", False)
+                                                                  and vp.tables()[2] == self.v_dim))
+        self.use_mma = (fast_ok and runtime.is_cuda
                         and ops.attention_mma_supported(runtime.dtype, self.head_dim, self.n_heads, self.n_kv_heads))
         # prefill on tcgen05 where that kernel takes the shape (bfloat16, head size 128, groups up to 32)
-        self.use_umma_prefill = (not self.general and runtime.is_cuda
+        self.use_umma_prefill = (fast_ok and runtime.is_cuda
                                  and ops.attention_umma_supported(runtime.dtype, self.head_dim, self.n_heads, self.n_kv_heads))
+        self.generic_attention = bool(getattr(runtime, "generic_attention", False))   # comparisons: the general kernels only
 
     def forward(self, x: torch.Tensor, ctx, view, writes_cache: bool = True) -> torch.Tensor:
         rt = self.runtime
@@ -176,6 +182,25 @@ class GQAttention:
         if self.value_position is not None:
             vcos, vsin, vrot = self.value_position.tables()
             vinter = bool(getattr(self.value_position, "interleaved", False))
+        where = (ctx.seq_qstart, ctx.seq_past, ctx.seq_slot, view.page_table, view.num_pages, view.k_pages, view.v_pages)
+        extra = dict(sink=self.sink, out_cos=vcos, out_sin=vsin)
+        if self.use_umma_prefill and not ctx.decode and not self.generic_attention:
+            ops.attention_umma_prefill(q, out, ctx.n_seqs, ctx.max_q, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
+                                       self.window, *where, self.runtime.status, **extra)
+            return
+        if self.use_mma and not self.generic_attention:
+            scratch = None
+            split_keys, max_splits, floor = SPLIT_KEYS, 0, 0
+            if ctx.decode:
+                split_keys, max_splits, floor = ops.attention_mma_decode_ranges(
+                    q.device, self.head_dim, ctx.n_seqs, self.n_kv_heads, ctx.max_kv_len, SPLIT_KEYS)
+                scratch = ctx.buffer(
+                    "attn.scratch",
+                    (ops.attention_generic_scratch_floats(ctx.n_seqs, self.n_heads, self.head_dim, max_splits),), torch.float32)
+            ops.attention_mma(ctx.decode, q, out, ctx.n_seqs, ctx.max_q, self.n_heads, self.n_kv_heads, self.head_dim,
+                              self.scale, self.window, *where, scratch, split_keys, max_splits, self.runtime.status,
+                              min_range_keys=floor, **extra)
+            return
         scratch = None
         max_splits = 0
         if ctx.decode:

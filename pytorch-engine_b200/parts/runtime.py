@@ -78,6 +78,7 @@ class Runtime:
         self._pending_next = 0
         self._adopted: Dict[Tuple[int, torch.dtype], torch.Tensor] = {}
         self.position_limit = None  # the longest sequence the engine holds: position tables need no more rows
+        self.generic_attention = os.environ.get("PE_B200_GENERIC_ATTENTION", "0") == "1"  # comparisons: no tensor-core attention
         self.gemm_backend = None  # a callable (x, weight, out, out_dtype) -> tensor or None that takes over products
         self.own_small_gemm = True  # products with few rows run on csrc/gemm_smallm.cu
         self.small_gemm_rows = 8    # up to this many rows (measured: beyond it the library product is faster)

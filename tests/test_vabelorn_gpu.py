@@ -267,6 +267,56 @@ def test_attention_with_values_of_their_own_size_against_the_formula(pe, dtype):
                 row += 1
 
 
+@pytest.mark.parametrize("d,nh,nkv", [(64, 8, 2), (128, 4, 2), (128, 6, 1)])
+def test_tensor_core_attention_with_sink_and_turned_outputs(pe, d, nh, nkv):
+    """The mma.sync kernels (prompt and single token) and the tcgen05 prompt kernel with a sink and outputs turned back,
+    against the float32-arithmetic kernel on the same bfloat16 cache; one key far back stands out for every query."""
+    ops = pe.kernels.ops
+    dtype = torch.bfloat16
+    lens, q_lens = [700, 130, 64, 1], [250, 130, 3, 1]
+    g = torch.Generator().manual_seed(d + nh)
+    pages = Pages(lens, nkv, d, d, dtype, seed=4)
+    q = torch.randn(sum(q_lens), nh, d, generator=g)
+    for b, n in enumerate(lens):
+        for pos in range(n):
+            k = torch.randn(nkv, d, generator=g)
+            if b == 0 and pos == 65:
+                k = k + 3.0 * q[200, ::nh // nkv]            # the far key that the first sequence's row 200 looks for
+            pages.put(b, pos, k.to(dtype), torch.randn(nkv, d, generator=g).to(dtype))
+    pages.cuda()
+    rt = pe.parts.Runtime(DEV, torch.float32)
+    vpos = pe.parts.lookup("position", "rope")({"rotary_dim": d, "theta": 5000.0, "max_positions": 1024, "style": "interleaved"}, {}, rt)
+    cos, sin, _ = vpos.tables()
+    scale = 1.0 / math.sqrt(d)
+    B = len(lens)
+    qstart = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    past = torch.tensor([n - ql for n, ql in zip(lens, q_lens)], dtype=torch.int32, device=DEV)
+    slots = torch.arange(B, dtype=torch.int32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    where = (qstart, past, slots, pages.table, pages.n_pages, pages.k, pages.v)
+    qd = q.view(sum(q_lens), nh * d).to(DEV, dtype)
+    want = _attend(pe, False, q.view(sum(q_lens), -1), lens, q_lens, pages, nh, nkv, d, d, scale, True, (cos, sin, d, True), dtype)
+    plain_softmax = _attend(pe, False, q.view(sum(q_lens), -1), lens, q_lens, pages, nh, nkv, d, d, scale, False, None, dtype)
+    assert (want - plain_softmax).abs().max() > 0.05          # sink and rotation do change the result
+    got = torch.full_like(qd, float("nan"))
+    ops.attention_mma(False, qd, got, B, max(q_lens), nh, nkv, d, scale, 0, *where, None, 0, 0, status, sink=True, out_cos=cos, out_sin=sin)
+    assert status.tolist()[0] == 0 and (got.float().cpu() - want).abs().max() < 2e-2
+    if ops.attention_umma_supported(dtype, d, nh, nkv):
+        got = torch.full_like(qd, float("nan"))
+        ops.attention_umma_prefill(qd, got, B, max(q_lens), nh, nkv, d, scale, 0, *where, status, sink=True, out_cos=cos, out_sin=sin)
+        assert status.tolist()[0] == 0 and (got.float().cpu() - want).abs().max() < 2e-2
+    # single tokens: every sequence's last row
+    sel = [sum(q_lens[:b + 1]) - 1 for b in range(B)]
+    one = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    past1 = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    split_keys, max_splits, floor = ops.attention_mma_decode_ranges(torch.device(DEV), d, B, nkv, 1024, 512)
+    scratch = torch.full((ops.attention_generic_scratch_floats(B, nh, d, max_splits),), float("nan"), device=DEV)
+    got = torch.full((B, nh * d), float("nan"), dtype=dtype, device=DEV)
+    ops.attention_mma(True, qd[sel].contiguous(), got, B, 1, nh, nkv, d, scale, 0, one, past1, slots, pages.table, pages.n_pages,
+                      pages.k, pages.v, scratch, split_keys, max_splits, status, min_range_keys=floor, sink=True, out_cos=cos, out_sin=sin)
+    assert status.tolist()[0] == 0 and (got.float().cpu() - want[sel]).abs().max() < 2e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_norm_rotation_and_append_of_q_k_v(pe, dtype):
     """q/k norm with weights, interleaved rotation of part of the head, values divided by their root mean square and
