@@ -1,0 +1,258 @@
+"""``python bench.py --archs``: the Vabelorn architecture beside the Qwen3 dense decoder at equal layer sizes.
+
+Random weights, bfloat16, one B200.  For each size: tokens/s of a 2,048-token prompt and of decode steps at batch 8
+(context 2,048) through ``ModelRunner.step``, for both architectures; then the kernels that only the new
+architecture has, each beside the like kernel of the Qwen3 path at the same shape, with the bytes each must move
+over its time as a fraction of the measured copy bandwidth (MEASURED_PEAKS.json).  Every timed loop works on
+weights or buffers larger than L2 or flushes L2 between iterations (``flush`` in the output says which).  One JSON
+line at the end; a table on standard error on the way.
+"""
+import importlib
+import json
+import math
+import sys
+
+SIZES = {
+    # width, heads, kv heads, head size, feed-forward, layers, vocabulary, wkv heads x size
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=6144, layers=4, vocab=32768, wkv_heads=32, wkv_dim=64),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, layers=4, vocab=65536, wkv_heads=64, wkv_dim=64),
+}
+YARN = {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+
+
+def vabelorn_config(pe, s):
+    att = {"type": "attention", "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+                                          "scale": 1.0 / math.sqrt(s["dim"]),
+                                          "rot": {"base": 1e6, "dims": s["dim"] // 2, "scaling": YARN}},
+           "mlp": {"kind": "dense", "ff": s["ff"]}}
+    wkv = {"type": "wkv", "mixer": {"heads": s["wkv_heads"], "dim": s["wkv_dim"], "decay_rank": 64},
+           "mlp": {"kind": "dense", "ff": s["ff"]}}
+    return pe.VabelornConfig.from_dict({"architecture": "Vabelorn", "vocab": s["vocab"], "width": s["width"], "logit_scale": 1.0,
+                                        "norm": {"eps": 1e-6}, "token_side": {"dim": 64},
+                                        "layers": [att if i % 2 == 0 else wkv for i in range(s["layers"])]})
+
+
+def qwen3_config(pe, s):
+    return pe.Qwen3Config.from_dict(dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=s["layers"], hidden_size=s["width"],
+                                         num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"], head_dim=s["dim"],
+                                         intermediate_size=s["ff"], vocab_size=s["vocab"], rope_theta=1e6, rms_norm_eps=1e-6,
+                                         tie_word_embeddings=True, max_position_embeddings=8192))
+
+
+def timed(torch, fn, steps, warmup, flush=None, graph=False):
+    """Milliseconds per call of ``fn``, CUDA events around each call.  ``graph``: the call is recorded once into a CUDA
+    graph and the replays are timed, which leaves the host's time to prepare a launch out of a kernel of a few
+    microseconds.  ``flush``: a buffer larger than L2 that is written before every timed call."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    run = fn
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.graph(g, stream=side):
+            fn()
+        torch.cuda.synchronize()
+        run = g.replay
+        run()
+    total = 0.0
+    for _ in range(steps):
+        if flush is not None:
+            flush.add_(1.0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / steps
+
+
+def model_speeds(pe, torch, cfg, prompt, batch, context, steps, warmup):
+    """(prompt tokens/s, decode tokens/s, kernels per decode step) through the step function."""
+    vocab = getattr(cfg, "vocab", None) or cfg.vocab_size
+    eng = pe.Engine.from_random(cfg, seed=0, dtype="bfloat16", max_context_len=context + 64,
+                                max_cache_tokens=(batch + 1) * (context + 64), max_batch=batch)
+    for g in eng.cache.groups:
+        for t in (g.storage, g.v_storage):
+            if t is not None:
+                t.normal_(0.0, 0.5)
+    gen = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, vocab, (prompt,), generator=gen).tolist()
+
+    def one_prompt():
+        s = eng.alloc_slot()
+        eng.runner.step([pe.StepEntry(s, toks, (prompt - 1,))], check=False)
+        eng.free_slot(s)
+
+    ms_prompt = timed(torch, one_prompt, max(3, steps // 8), 3)
+    slots = [eng.alloc_slot() for _ in range(batch)]
+    start = context - steps - warmup - 1
+    for s in slots:
+        eng.cache.reserve(s, start)
+        eng.cache.commit(s, start)
+    dec = torch.randint(0, vocab, (steps + warmup + 1, batch), generator=gen).tolist()
+    it = iter(range(steps + warmup + 1))
+
+    def one_step():
+        i = next(it)
+        eng.runner.step([pe.StepEntry(s, (dec[i][j],), (0,)) for j, s in enumerate(slots)], check=False)
+
+    one_step()
+    ops = pe.kernels.ops
+    for _ in range(warmup - 1):
+        one_step()
+    torch.cuda.synchronize()
+    n0 = ops.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one_step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_step = e0.elapsed_time(e1) / steps
+    launches = (ops.launch_count() - n0) / steps
+    eng.runtime.raise_on_status()
+    weights = eng.model.weight_bytes()
+    del eng
+    torch.cuda.empty_cache()
+    return {"prompt_tokens_per_s": round(prompt / ms_prompt * 1e3), "prompt_ms": round(ms_prompt, 3),
+            "decode_tokens_per_s": round(batch / ms_step * 1e3), "decode_ms_per_step": round(ms_step, 4),
+            "kernels_per_decode_step": round(launches, 1), "weight_mib": round(weights / 2 ** 20)}
+
+
+def kernel_pairs(pe, torch, s, hbm_gbs, prompt, batch, context):
+    """The new kernels beside the like kernels of the Qwen3 path at the same shape: microseconds, and the bytes
+    each must move over its time as a fraction of the copy bandwidth."""
+    ops = pe.kernels.ops
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    H, G, d, width = s["heads"], s["kv_heads"], s["dim"], s["width"]
+    flush = torch.zeros(96 * 2 ** 20, device=dev)            # 384 MB written between iterations: three times L2
+    rt = pe.parts.Runtime(dev, bf)
+    rope = pe.parts.lookup("position", "rope")
+    pos_q = rope({"rotary_dim": d, "theta": 1e6, "max_positions": context + 64}, {}, rt)
+    pos_qi = rope({"rotary_dim": d // 2, "theta": 1e6, "max_positions": context + 64, "style": "interleaved", "scaling": YARN}, {}, rt)
+    pos_v = rope({"rotary_dim": d, "theta": 1e6, "max_positions": context + 64, "style": "interleaved"}, {}, rt)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    out = {}
+
+    def us_of(fn):
+        return 1e3 * timed(torch, fn, 20, 5, flush, graph=True)
+
+    def frac(nbytes, us):
+        return round(nbytes / (us * 1e-6) / (hbm_gbs * 1e9), 3)
+
+    def entry(name, us_new, us_like, nbytes, like):
+        out[name] = {"us": round(us_new, 2), "of_copy_peak": frac(nbytes, us_new), "like_kernel": like,
+                     "like_us": round(us_like, 2), "like_of_copy_peak": frac(nbytes, us_like),
+                     "times_as_far_from_roofline": round(us_new / us_like, 2)}
+
+    for what, n_seqs, q_len, past in (("prompt", 1, prompt, 0), ("decode", batch, 1, context - 1)):
+        n = n_seqs * q_len
+        length = past + q_len
+        pages_per = -(-length // 64)
+        n_pages = n_seqs * pages_per
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(n_seqs, pages_per).contiguous()
+        kp = torch.randn(n_pages, G, 64, d, device=dev).to(bf)
+        vp = torch.randn(n_pages, G, 64, d, device=dev).to(bf)
+        qstart = torch.arange(0, n + 1, q_len, dtype=torch.int32, device=dev)
+        pasts = torch.full((n_seqs,), past, dtype=torch.int32, device=dev)
+        slots = torch.arange(n_seqs, dtype=torch.int32, device=dev)
+        token_seq = torch.arange(n_seqs, dtype=torch.int32, device=dev).repeat_interleave(q_len).contiguous()
+        token_pos = (torch.arange(q_len, dtype=torch.int32, device=dev)[None] + past).repeat(n_seqs, 1).view(-1).contiguous()
+        qkv = torch.randn(n, (H + 2 * G) * d, device=dev).to(bf)
+        qw, kw = torch.ones(d, device=dev), torch.ones(d, device=dev)
+        where = (token_seq, token_pos, slots, qstart, table, n_pages, kp, vp)
+        cq, sq, _ = pos_q.tables()
+        ci, si, ri = pos_qi.tables()
+        cv, sv, rv = pos_v.tables()
+        # norm + rotation + append
+        new = lambda: ops.qkv_rotate_append(qkv, n, H, G, d, d, qw, kw, 1e-6, ci, si, ri, True, True, cv, sv, rv, True, *where, True, status)
+        like = lambda: ops.qk_norm_rope_append(qkv, n, H, G, d, qw, kw, 1e-6, cq, sq, d, *where, True, status)
+        nbytes = n * (H + 2 * G) * d * 2 + n * (H + G) * d * 2 + n * 2 * G * d * 2        # rows in, q and k back, k and v to the cache
+        entry(f"{what}: q/k/v norm, rotation, append", us_of(new), us_of(like), nbytes,
+              "qk_norm_rope_append")
+        # attention
+        o = torch.empty(n, H * d, dtype=bf, device=dev)
+        nbytes = n * H * d * 2 * 2 + n_seqs * length * 2 * G * d * 2
+        if what == "prompt":
+            new = lambda: ops.attention_umma_prefill(qkv, o, n_seqs, q_len, H, G, d, 0.088, 0, qstart, pasts, slots, table, n_pages, kp, vp,
+                                                     status, sink=True, out_cos=cv, out_sin=sv)
+            like = lambda: ops.attention_umma_prefill(qkv, o, n_seqs, q_len, H, G, d, 0.088, 0, qstart, pasts, slots, table, n_pages, kp, vp, status)
+            name = "attention_umma_prefill"
+        else:
+            sk, ms, fl = ops.attention_mma_decode_ranges(dev, d, n_seqs, G, context + 64, 512)
+            scratch = torch.empty(ops.attention_generic_scratch_floats(n_seqs, H, d, ms), device=dev)
+            new = lambda: ops.attention_mma(True, qkv, o, n_seqs, 1, H, G, d, 0.088, 0, qstart, pasts, slots, table, n_pages, kp, vp, scratch,
+                                            sk, ms, status, min_range_keys=fl, sink=True, out_cos=cv, out_sin=sv)
+            like = lambda: ops.attention_mma(True, qkv, o, n_seqs, 1, H, G, d, 0.088, 0, qstart, pasts, slots, table, n_pages, kp, vp, scratch,
+                                             sk, ms, status, min_range_keys=fl)
+            name = "attention_mma (split + merge)"
+        entry(f"{what}: attention with sink, outputs turned back", us_of(new), us_of(like), nbytes, name)
+        # norm on the sublayer's output, then the add
+        stream = torch.randn(n, width, device=dev)
+        delta = torch.randn(n, width, device=dev).to(bf)
+        w = torch.ones(width, device=dev)
+        cast = torch.empty(n, width, dtype=bf, device=dev)
+        new = lambda: ops.rmsnorm_add(stream, delta, w, 1e-6, cast)
+        like = lambda: ops.rmsnorm_residual(stream, delta, w, cast, 1e-6)
+        entry(f"{what}: norm of the output, add, copy in bfloat16", us_of(new), us_of(like),
+              n * width * (4 + 4 + 2 + 2), "rmsnorm_residual")
+        # the recurrence: no like kernel in the Qwen3 path; held against the bytes it must move
+        WH, wd = s["wkv_heads"], s["wkv_dim"]
+        hd = WH * wd
+        r, k, v, g = (torch.randn(n, hd, device=dev).to(bf) for _ in range(4))
+        k.mul_(0.3)
+        wlin = torch.randn(n, hd, device=dev)
+        w0, u, gn = torch.zeros(hd, device=dev), torch.zeros(hd, device=dev), torch.ones(hd, device=dev)
+        res = torch.empty(n, hd, dtype=bf, device=dev)
+        state = torch.zeros(n_seqs, WH, wd, wd, device=dev)
+        prev = torch.zeros(n_seqs, width, device=dev)
+        x = torch.randn(n, width, device=dev).to(bf)
+        chunk, max_chunks, scratch = 0, 1, None
+        if q_len > 128:
+            chunk, max_chunks = 64, -(-q_len // 64)
+            scratch = torch.empty(ops.wkv_scratch_floats(n_seqs, WH, wd, max_chunks), device=dev)
+        new = lambda: ops.wkv_recurrence(r, k, v, g, wlin, w0, u, gn, 1e-6, res, state, prev, x, slots, qstart, n_seqs, q_len, WH, wd,
+                                         chunk, max_chunks, scratch, status)
+        us = us_of(new)
+        nbytes = n * hd * (4 * 2 + 4 + 2) + n_seqs * WH * wd * wd * 4 * 2
+        flops = n * WH * wd * wd * 5 * (2 if chunk else 1)
+        out[f"{what}: wkv recurrence, head norm, gate"] = {"us": round(us, 2), "of_copy_peak": frac(nbytes, us), "like_kernel": None,
+                                                           "float32_gflops": round(flops / us / 1e3, 1)}
+        mixes = torch.empty(5, n, width, dtype=bf, device=dev)
+        mu = torch.rand(5, width, device=dev)
+        new = lambda: ops.token_shift_mix(x, mu, prev, token_seq, slots, qstart, mixes, status)
+        us = us_of(new)
+        out[f"{what}: token shift, five mixes"] = {"us": round(us, 2), "of_copy_peak": frac(n * width * 2 * 6, us), "like_kernel": None}
+    return out
+
+
+def main(args):
+    import torch
+
+    sys.path.insert(0, __file__.rsplit("/", 1)[0])
+    import bench
+
+    pe = importlib.import_module("pytorch-engine_b200")
+    peaks = bench.load_peaks()
+    prompt, batch, context = args.prefill_tokens, args.batch, min(args.context, 2048)
+    result = {"metric": "vabelorn_beside_qwen3", "dtype": "bf16", "data": "synthetic (random weights)", "peaks": peaks,
+              "prompt_tokens": prompt, "decode_batch": batch, "decode_context": context,
+              "flush": "model runs: weights larger than L2; kernel pairs: 384 MB written between iterations", "sizes": {}}
+    names = [n for n in SIZES if not args.arch_sizes or n in args.arch_sizes.split(",")]
+    for name in names:
+        s = SIZES[name]
+        row = {"shape": s}
+        for arch, cfg in (("vabelorn", vabelorn_config(pe, s)), ("qwen3", qwen3_config(pe, s))):
+            row[arch] = model_speeds(pe, torch, cfg, prompt, batch, context, args.steps, max(args.warmup, 3))
+            print(f"[{name}] {arch}: {row[arch]}", file=sys.stderr, flush=True)
+        row["kernels"] = kernel_pairs(pe, torch, s, peaks["hbm_gbs"], prompt, batch, context)
+        for k, v in row["kernels"].items():
+            print(f"[{name}] {k}: {v}", file=sys.stderr, flush=True)
+        result["sizes"][name] = row
+    result["gpu_launches"] = pe.kernels.ops.launch_count()
+    print(json.dumps(result))
+    return 0

@@ -156,6 +156,41 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ stream, const T* delta, c
   }
 }
 
+// The same with 4-element accesses, for widths that are a multiple of 4 and 16-byte aligned rows.
+template <typename T>
+__global__ void __launch_bounds__(1024) rmsnorm_add_vec4_kernel(float* __restrict__ stream, const T* delta,
+                                                                 const float* __restrict__ weight, T* __restrict__ cast,
+                                                                 int n_rows, int dim, float eps) {
+  extern __shared__ float row_buf[];  // dim floats
+  __shared__ float red[32];
+  const int c0 = threadIdx.x * 4;
+  float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c0 < dim) w0 = Vec4<float>::load(weight + c0);       // the weight does not come from the kernel before this one
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  if (r >= n_rows) return;
+  const T* d_row = delta + (size_t)r * dim;
+  float* s_row = stream + (size_t)r * dim;
+  float ss = 0.f;
+  float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c0 < dim) s0 = Vec4<float>::load(s_row + c0);        // the stream's first piece is on its way during the reduction
+  for (int c = c0; c < dim; c += blockDim.x * 4) {
+    const float4 y = Vec4<T>::load(d_row + c);
+    *reinterpret_cast<float4*>(row_buf + c) = y;
+    ss += y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)dim + eps);
+  for (int c = c0; c < dim; c += blockDim.x * 4) {
+    const float4 y = *reinterpret_cast<const float4*>(row_buf + c);
+    const float4 w = c == c0 ? w0 : Vec4<float>::load(weight + c);
+    float4 h = c == c0 ? s0 : Vec4<float>::load(s_row + c);
+    h.x += y.x * inv * w.x; h.y += y.y * inv * w.y; h.z += y.z * inv * w.z; h.w += y.w * inv * w.w;
+    Vec4<float>::store(s_row + c, h);
+    if (cast) Vec4<T>::store(cast + (size_t)r * dim + c, h);
+  }
+}
+
 template <typename K>
 static int set_smem(K kernel, size_t bytes) {
   if (bytes > 48 * 1024) {
@@ -225,14 +260,17 @@ extern "C" int pe_rmsnorm_add(int dtype, float* stream, const void* delta, const
   if (dim <= 0) return PE_ERR_BAD_ARGUMENT;
   const size_t smem = (size_t)dim * sizeof(float);
   if (smem > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;
-  const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+  int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+  const bool vec = (dim % 4 == 0) && ((uintptr_t)stream % 16 == 0) && ((uintptr_t)weight % 16 == 0) &&
+                   ((uintptr_t)cast % 16 == 0) && ((uintptr_t)delta % 16 == 0);
+  if (vec && n_rows <= 64 && dim > 2048) threads = 1024;   // a handful of rows: latency counts (see pe_rmsnorm_residual)
   int e;
   if (dtype == PE_F32) {
-    auto k = pe::rmsnorm_add_kernel<float>;
+    auto k = vec ? pe::rmsnorm_add_vec4_kernel<float> : pe::rmsnorm_add_kernel<float>;
     if ((e = pe::set_smem(k, smem))) return e;
     pe::launch(k, n_rows, threads, smem, stream_, stream, (const float*)delta, weight, (float*)cast, n_rows, dim, eps);
   } else if (dtype == PE_BF16) {
-    auto k = pe::rmsnorm_add_kernel<__nv_bfloat16>;
+    auto k = vec ? pe::rmsnorm_add_vec4_kernel<__nv_bfloat16> : pe::rmsnorm_add_kernel<__nv_bfloat16>;
     if ((e = pe::set_smem(k, smem))) return e;
     pe::launch(k, n_rows, threads, smem, stream_, stream, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)cast, n_rows, dim, eps);
   } else {

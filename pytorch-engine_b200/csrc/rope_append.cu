@@ -479,6 +479,135 @@ __global__ void qkv_rotate_append_kernel(QkvRotateArgs a) {
   for (int c = rot + lane; c < D; c += 32) put(c, value(c));
 }
 
+// The general form for bfloat16 rows with 16-byte accesses: keys and values of one size that is a multiple of 8 (up to
+// 256), interleaved pairs, rotated sizes that are multiples of 8, everything 16-byte aligned.  A head takes
+// head_dim / 8 lanes; a lane's eight features are four whole pairs, so the rotation needs no other lane.  A block takes
+// TPB tokens and has all their rows and positions in flight before it uses the first.
+template <int TPB>
+__global__ void __launch_bounds__(256, 4) qkv_rotate_append_vec8_kernel(QkvRotateArgs a, int lanes_per_head) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  typedef __nv_bfloat16 T;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int lph = lanes_per_head, heads_per_warp = 32 / lph;
+  const int sub = lane / lph, li = lane - sub * lph;
+  const int total_heads = a.n_heads + 2 * a.n_kv_heads;
+  const int head = (blockIdx.y * (blockDim.x >> 5) + warp) * heads_per_warp + sub;
+  const bool active = sub < heads_per_warp && head < total_heads;
+  const int d = a.head_dim;
+  const bool is_q = head < a.n_heads;
+  const bool is_k = !is_q && head < a.n_heads + a.n_kv_heads;
+  const bool is_v = !is_q && !is_k;
+  const int kv_head = is_k ? head - a.n_heads : head - a.n_heads - a.n_kv_heads;
+  const bool pow2 = (lph & (lph - 1)) == 0;
+  const float* w = is_q ? a.q_norm_w : (is_k ? a.k_norm_w : nullptr);
+  const bool normed = is_v ? (a.v_unit_norm != 0) : (w != nullptr);
+  const float* ct = is_v ? a.v_cos : a.cos_table;
+  const float* st = is_v ? a.v_sin : a.sin_table;
+  const int rot = ct ? (is_v ? a.v_rotary_dim : a.rotary_dim) : 0;
+  const int rows = is_v ? a.v_table_rows : a.table_rows;
+  const int half = rot / 2;
+  const bool turns = active && 8 * li < rot;
+  float wv[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) wv[e] = 1.f;
+  if (active && w) {
+    const float4 w0 = *reinterpret_cast<const float4*>(w + 8 * li), w1 = *reinterpret_cast<const float4*>(w + 8 * li + 4);
+    wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+  }
+  uint4 raws[TPB];
+  int poss[TPB];
+#pragma unroll
+  for (int i = 0; i < TPB; ++i) {
+    const int t = blockIdx.x * TPB + i;
+    raws[i] = make_uint4(0, 0, 0, 0);
+    poss[i] = -1;
+    if (t < a.n_tokens) {
+      if (active) raws[i] = *reinterpret_cast<const uint4*>((const T*)a.qkv + (size_t)t * a.ld + (size_t)head * d + 8 * li);
+      poss[i] = a.token_pos[t];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < TPB; ++i) {
+    const int t = blockIdx.x * TPB + i;
+    if (t >= a.n_tokens) break;
+    T* row = (T*)a.qkv + (size_t)t * a.ld + (size_t)head * d + 8 * li;
+    const int pos = poss[i];
+    T* cache_row = nullptr;
+    if (active && !is_q && a.write_cache) {
+      const int b = a.token_seq[t];
+      const int slot = a.seq_slot[b];
+      const int logical = pos / kPageTokens;
+      if (pos < 0 || logical >= a.table_stride) {
+        if (li == 0) report(a.status, kStatusPositionOutOfRange, t, pos, a.table_stride * kPageTokens);
+      } else {
+        const int page = a.page_table[(size_t)slot * a.table_stride + logical];
+        if (page < 0 || page >= a.num_pages) {
+          if (li == 0) report(a.status, kStatusPageOutOfRange, t, page, a.num_pages);
+        } else {
+          T* base = (T*)(is_k ? a.k_pages : a.v_pages);
+          const int off = pos % kPageTokens;
+          T* head_row = base + (((size_t)page * a.n_kv_heads + kv_head) * kPageTokens + off) * d;
+          cache_row = head_row + 8 * li;
+          const int q_end = a.seq_qstart[b + 1];
+          if (t + 1 == q_end && off + 1 < kPageTokens && (off == 0 || q_end - a.seq_qstart[b] > 1)) {
+            uint4* r4 = reinterpret_cast<uint4*>(head_row + d);      // clear the rest of the page (see the first kernel)
+            const size_t n4 = (size_t)(kPageTokens - 1 - off) * d / 8;
+            for (size_t x = li; x < n4; x += lph) r4[x] = make_uint4(0, 0, 0, 0);
+          }
+        }
+      }
+    }
+    float x[8];
+    {
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raws[i]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        x[2 * e] = f.x;
+        x[2 * e + 1] = f.y;
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+    if (pow2) {
+      for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    } else {
+      float total = 0.f;
+      for (int l = 0; l < lph; ++l) total += __shfl_sync(0xffffffffu, ss, (sub * lph + l) & 31);
+      ss = total;
+    }
+    if (!active) continue;
+    if (normed) {
+      const float inv = rsqrtf(ss / (float)d + a.eps);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = x[e] * inv * wv[e];
+    }
+    if (turns) {
+      if (pos < 0 || pos >= rows) {
+        if (li == 0) report(a.status, kStatusPositionOutOfRange, t, pos, rows);
+        continue;
+      }
+      const float4 c4 = *reinterpret_cast<const float4*>(ct + (size_t)pos * half + 4 * li);
+      const float4 s4 = *reinterpret_cast<const float4*>(st + (size_t)pos * half + 4 * li);
+      const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float x0 = x[2 * e], x1 = x[2 * e + 1];
+        x[2 * e] = x0 * cc[e] - x1 * sn[e];
+        x[2 * e + 1] = x1 * cc[e] + x0 * sn[e];
+      }
+    }
+    uint4 out;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(x[2 * e], x[2 * e + 1]);
+    if (!is_v) *reinterpret_cast<uint4*>(row) = out;
+    if (cache_row) *reinterpret_cast<uint4*>(cache_row) = out;
+  }
+}
+
 }  // namespace pe
 
 extern "C" int pe_batch_expand(const int* seq_qstart, const int* seq_past, int n_seqs, int* token_seq, int* token_pos,
@@ -567,6 +696,21 @@ extern "C" int pe_qkv_rotate_append(int dtype, void* qkv, long long ld, int n_to
   const int warps = 4;
   dim3 grid(n_tokens, (n_heads + 2 * n_kv_heads + warps - 1) / warps);
   if (grid.y > 65535) return PE_ERR_UNSUPPORTED_SIZE;
+  auto al16 = [](const void* p) { return (uintptr_t)p % 16 == 0; };
+  const bool vec8 = dtype == PE_BF16 && head_dim == v_dim && head_dim % 8 == 0 && head_dim <= 256 && ld % 8 == 0 &&
+                    (a.rotary_dim == 0 || (interleaved && a.rotary_dim % 8 == 0)) &&
+                    (a.v_rotary_dim == 0 || (v_interleaved && a.v_rotary_dim % 8 == 0)) && al16(qkv) && al16(k_pages) &&
+                    al16(v_pages) && al16(cos_table) && al16(sin_table) && al16(v_cos) && al16(v_sin) && al16(q_norm_w) &&
+                    al16(k_norm_w);
+  if (vec8 && n_tokens >= 256) {   // as for the kernel it stands beside: with a few tokens the one-warp-a-head form is faster
+    constexpr int kTokensPerBlock = 4;
+    const int lph = head_dim / 8, heads_per_block = 8 * (32 / lph);
+    dim3 g((n_tokens + kTokensPerBlock - 1) / kTokensPerBlock, (n_heads + 2 * n_kv_heads + heads_per_block - 1) / heads_per_block);
+    if (g.y > 65535) return PE_ERR_UNSUPPORTED_SIZE;
+    pe::launch(pe::qkv_rotate_append_vec8_kernel<kTokensPerBlock>, g, 256, 0, stream, a, lph);
+    PE_LAUNCH_CHECK();
+    return PE_OK;
+  }
   if (dtype == PE_F32) pe::launch(pe::qkv_rotate_append_kernel<float>, grid, warps * 32, 0, stream, a);
   else if (dtype == PE_BF16) pe::launch(pe::qkv_rotate_append_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream, a);
   else return PE_ERR_UNSUPPORTED_DTYPE;

@@ -7,8 +7,8 @@
 //   update          S     <- diag(w[t]) S + k[t] v[t]^T              float32 state [d_key, d_value] per head
 //   out[t]          = o[t] / rms(o[t]) * gnorm * silu(g[t])          per head, eps inside the root
 //
-// The state's columns (value channels) never mix: thread j of a block owns column j of its head's state in
-// registers and walks the sequence's tokens of this step in order.  The recurrence, the decay and the head norm are
+// A block owns one head's state in registers and walks the sequence's tokens of this step in order (the read is
+// written as o_j = sum_i r_i S_ij + v_j sum_i r_i u_i k_i, the bonus term taken out of the sum over i).  The recurrence, the decay and the head norm are
 // float32 whatever the run dtype; r, k, v, g come from matrix products in the run dtype.  Long prompts are cut into
 // chunks that run side by side: the update is linear in S, so a chunk first folds its tokens into a state that
 // starts at zero together with the product of its decays, a second kernel chains the chunks' starts
@@ -43,6 +43,66 @@ __global__ void token_shift_mix_kernel(const T* x, const float* __restrict__ mu,
     const float dlt = hp - h;
     for (int s = 0; s < n_mix; ++s)
       out[((size_t)s * n_tokens + t) * width + c] = from_f32<T>(fmaf(dlt, mu[(size_t)s * width + c], h));
+  }
+}
+
+// The same for bfloat16 rows whose width is a multiple of 8 and that start on 16-byte boundaries: eight channels a
+// thread, 16-byte loads and stores.
+__global__ void token_shift_mix_vec8_kernel(const __nv_bfloat16* x, const float* __restrict__ mu, int n_mix,
+                                            const float* prev_state, const int* token_seq, const int* seq_slot,
+                                            const int* seq_qstart, __nv_bfloat16* __restrict__ out, int n_tokens, int width,
+                                            int n_slots, int* status) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  if (t >= n_tokens) return;
+  const int b = token_seq[t];
+  const bool first = t == seq_qstart[b];
+  const int slot = seq_slot[b];
+  if (first && (slot < 0 || slot >= n_slots)) {
+    if (threadIdx.x == 0) report(status, kStatusSlotOutOfRange, t, slot, n_slots);
+    return;
+  }
+  const __nv_bfloat16* cur = x + (size_t)t * width;
+  for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
+    float h[8], dl[8];
+    {
+      const uint4 raw = *reinterpret_cast<const uint4*>(cur + c);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        h[2 * e] = f.x;
+        h[2 * e + 1] = f.y;
+      }
+    }
+    if (first) {
+      const float4 p0 = *reinterpret_cast<const float4*>(prev_state + (size_t)slot * width + c);
+      const float4 p1 = *reinterpret_cast<const float4*>(prev_state + (size_t)slot * width + c + 4);
+      const float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dl[e] = pp[e] - h[e];
+    } else {
+      const uint4 raw = *reinterpret_cast<const uint4*>(cur + c - width);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        dl[2 * e] = f.x - h[2 * e];
+        dl[2 * e + 1] = f.y - h[2 * e + 1];
+      }
+    }
+    for (int s = 0; s < n_mix; ++s) {
+      const float4 m0 = *reinterpret_cast<const float4*>(mu + (size_t)s * width + c);
+      const float4 m1 = *reinterpret_cast<const float4*>(mu + (size_t)s * width + c + 4);
+      const float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+      uint4 o;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        o2[e] = __floats2bfloat162_rn(fmaf(dl[2 * e], mm[2 * e], h[2 * e]), fmaf(dl[2 * e + 1], mm[2 * e + 1], h[2 * e + 1]));
+      *reinterpret_cast<uint4*>(out + ((size_t)s * n_tokens + t) * width + c) = o;
+    }
   }
 }
 
@@ -81,19 +141,50 @@ struct WkvArgs {
 // MODE 1: chunk c from a zero state: leaves its end state and decay product           (no outputs)
 // MODE 3: chunk c from its true start (chunk_state, as the chain kernel left it): writes outputs; the last chunk
 //         writes the slot's state, which no block of this launch reads
+//
+// A block holds one head's state in registers, a tile of 4 columns x RI rows per thread (the DMAX / 4 column blocks
+// times NIB row blocks are the block's threads).  It walks its tokens in batches of TB: all threads stage the batch's
+// r, k, w (the decay itself, exponentials taken here) and v in shared memory with the batch's loads in flight
+// together; then every thread runs the batch's tokens through its tile: three multiply-adds per state element and
+// token, with r, k, w of its row block read as 16-byte pieces that serve four columns each (a thread that owned a
+// whole column read twelve bytes of shared memory per state element and was bound by that), the partial outputs of
+// the row blocks added up by shuffles and left in shared memory; the per-head norm, the gate and the store are then
+// done a token per warp.  The bonus term is the same number for every column, sum_i r_i u_i k_i times v_j, so it is
+// summed once per token.  Barriers per batch, not per token.  Row blocks lie 4 floats apart from a multiple of 32 in
+// shared memory, so that the four (or eight) pieces a warp reads at once fall into different banks.
+template <int DMAX> struct WkvTile {
+  static constexpr int NIB = DMAX <= 128 ? 4 : 8;     // row blocks
+  static constexpr int RI = DMAX / NIB;               // rows per thread
+  static constexpr int NJB = DMAX / 4;                // column blocks
+  static constexpr int NT = NJB * NIB;                // threads per block
+  static constexpr int TB = DMAX <= 64 ? 16 : (DMAX == 128 ? 8 : 4);   // tokens per batch (shared memory: under 48 KB, and eight blocks an SM at 64)
+  static constexpr int RS = RI + 4;                   // floats from one row block to the next in shared memory
+  static constexpr int ROWW = NIB * RS;
+  static constexpr int MIN_BLOCKS = DMAX <= 32 ? 16 : (DMAX == 64 ? 8 : (DMAX == 128 ? 2 : 1));
+};
+
 template <typename T, int DMAX, int MODE>
-__global__ void __launch_bounds__(DMAX) wkv_scan_kernel(WkvArgs a) {
-  __shared__ float sr[2][DMAX], sk[2][DMAX], sw[2][DMAX], su[DMAX], red[32];
-  const int j = threadIdx.x, d = a.d;
+__global__ void __launch_bounds__(WkvTile<DMAX>::NT, MODE == 0 ? 1 : WkvTile<DMAX>::MIN_BLOCKS) wkv_scan_kernel(WkvArgs a) {
+  typedef WkvTile<DMAX> TL;
+  constexpr int NIB = TL::NIB, RI = TL::RI, NT = TL::NT, TB = TL::TB, RS = TL::RS, NW = NT / 32;
+  __shared__ __align__(16) float sr[TB][TL::ROWW], sk[TB][TL::ROWW], sw[TB][TL::ROWW];
+  __shared__ __align__(16) float sv[TB][DMAX], so[TB][DMAX];
+  __shared__ float sg[MODE == 1 ? 1 : TB][DMAX];      // silu(g) times the norm's weight
+  __shared__ float sc[TB];
+  const int tid = threadIdx.x, d = a.d;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int ib = tid % NIB, jb = tid / NIB;          // this thread's row block and column block
   const int head = blockIdx.x, b = blockIdx.y, c = blockIdx.z;
   const int hd = a.heads * d;
-  const int col = head * d + j;
-  const bool live = j < d;
-  // constants of the head: on their way before the wait
-  float w0 = 0.f, gn = 0.f;
+  // as a stager, thread `tid` brings channel `tid` of the head (the first DMAX threads do)
+  const bool stager = tid < DMAX;
+  const bool live = tid < d;
+  const int col = head * d + tid;
+  const int spos = (tid / RI) * RS + (tid % RI);     // where channel `tid` lies in a row of sr, sk, sw
+  float w0 = 0.f, uj = 0.f, gn = 0.f;
   if (live) {
     w0 = a.w0[col];
-    su[j] = a.u[col];
+    uj = a.u[col];
     gn = a.gnorm[col];
   }
   pdl_wait_block();
@@ -108,102 +199,192 @@ __global__ void __launch_bounds__(DMAX) wkv_scan_kernel(WkvArgs a) {
   }
   const int slot = a.seq_slot[b];
   if (slot < 0 || slot >= a.n_slots) {
-    if (j == 0) report(a.status, kStatusSlotOutOfRange, b, slot, a.n_slots);
+    if (tid == 0) report(a.status, kStatusSlotOutOfRange, b, slot, a.n_slots);
     return;
   }
-  float S[DMAX];
   float* slot_state = a.state + ((size_t)slot * a.heads + head) * d * d;
   float* cs = (MODE != 0) ? a.chunk_state + (((size_t)b * a.max_chunks + c) * a.heads + head) * d * d : nullptr;
   const float* start = (MODE == 0) ? slot_state : cs;
+  const int row0 = ib * RI, col0 = 4 * jb;
+  const bool vec_state = (d % 4 == 0);
+  float S[4][RI];                         // S[cc][r]: state element (row0 + r, col0 + cc)
 #pragma unroll
-  for (int i = 0; i < DMAX; ++i) S[i] = (MODE != 1 && live && i < d) ? start[(size_t)i * d + j] : 0.f;
-  float decay_prod = 1.f;   // MODE 1: thread i keeps the product of w[.][i]
-  const T* R = (const T*)a.r; const T* K = (const T*)a.k; const T* V = (const T*)a.v; const T* G = (const T*)a.g;
-  auto stage = [&](int t, int buf) {
-    if (live) {
-      const size_t at = (size_t)t * a.ld + col;
-      sr[buf][j] = to_f32<T>(R[at]);
-      sk[buf][j] = to_f32<T>(K[at]);
-      sw[buf][j] = expf(-expf(a.wlin[(size_t)t * hd + col] + w0));
-    }
-  };
-  stage(t0, 0);
-  for (int t = t0; t < t1; ++t) {
-    const int buf = (t - t0) & 1;
-    __syncthreads();                       // this token's r, k, w are staged; the other buffer is free
-    if (t + 1 < t1) stage(t + 1, buf ^ 1);
-    const float vj = live ? to_f32<T>(V[(size_t)t * a.ld + col]) : 0.f;
-    if (MODE == 1) {
-      if (live) decay_prod *= sw[buf][j];
-#pragma unroll
-      for (int i = 0; i < DMAX; ++i)
-        if (i < d) S[i] = fmaf(sw[buf][i], S[i], sk[buf][i] * vj);
-      continue;
-    }
-    float o = 0.f;
-#pragma unroll
-    for (int i = 0; i < DMAX; ++i) {
-      if (i < d) {
-        const float kv = sk[buf][i] * vj;
-        o = fmaf(sr[buf][i], fmaf(su[i], kv, S[i]), o);
-        S[i] = fmaf(sw[buf][i], S[i], kv);
+  for (int r = 0; r < RI; ++r) {
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (MODE != 1 && row0 + r < d) {
+      const float* p = start + (size_t)(row0 + r) * d + col0;
+      if (vec_state) {
+        if (col0 < d) x = *reinterpret_cast<const float4*>(p);
+      } else {
+        if (col0 < d) x.x = p[0];
+        if (col0 + 1 < d) x.y = p[1];
+        if (col0 + 2 < d) x.z = p[2];
+        if (col0 + 3 < d) x.w = p[3];
       }
     }
-    // the head's outputs divided by their root mean square, times the norm's weight and the gate
-    const float ss = block_sum(live ? o * o : 0.f, red);
-    if (live) {
-      const float inv = rsqrtf(ss / (float)d + a.eps);
-      const float gl = to_f32<T>(G[(size_t)t * a.ld + col]);
-      const float gate = gl / (1.f + expf(-gl));
-      ((T*)a.out)[(size_t)t * hd + col] = from_f32<T>(o * inv * gn * gate);
+    S[0][r] = x.x; S[1][r] = x.y; S[2][r] = x.z; S[3][r] = x.w;
+  }
+  float decay_prod = 1.f;   // MODE 1: stager `tid` keeps the product of its channel's decays
+  const T* R = (const T*)a.r; const T* K = (const T*)a.k; const T* V = (const T*)a.v; const T* G = (const T*)a.g;
+  for (int tb = t0; tb < t1; tb += TB) {
+    const int nt = min(TB, t1 - tb);
+    __syncthreads();                       // the batch before this one has been read to its end
+    if (stager) {
+#pragma unroll
+      for (int t4 = 0; t4 < TB; t4 += 4) {  // four tokens' loads in flight at a time
+        float rr[4], kk[4], ww[4], vv[4], gg[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tt = t4 + e;
+          rr[e] = kk[e] = vv[e] = ww[e] = gg[e] = 0.f;
+          if (live && tt < nt) {
+            const size_t at = (size_t)(tb + tt) * a.ld + col;
+            rr[e] = to_f32<T>(R[at]);
+            kk[e] = to_f32<T>(K[at]);
+            vv[e] = to_f32<T>(V[at]);
+            if (MODE != 1) gg[e] = to_f32<T>(G[at]);
+            ww[e] = a.wlin[(size_t)(tb + tt) * hd + col];
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tt = t4 + e;
+          const float w = (live && tt < nt) ? expf(-expf(ww[e] + w0)) : 0.f;
+          sr[tt][spos] = rr[e];             // channels beyond d hold zeros: their rows of the state stay zero
+          sk[tt][spos] = kk[e];
+          sw[tt][spos] = w;
+          sv[tt][tid] = vv[e];
+          if (MODE == 1) {
+            if (live && tt < nt) decay_prod *= w;
+          } else {
+            so[tt][tid] = rr[e] * uj * kk[e];
+            sg[tt][tid] = gg[e] / (1.f + expf(-gg[e])) * gn;
+          }
+        }
+      }
+    }
+    __syncthreads();
+    if (MODE != 1) {                       // the bonus: one number per token
+      for (int tt = warp; tt < nt; tt += NW) {
+        float sum = 0.f;
+        for (int i = lane; i < d; i += 32) sum += so[tt][i];
+        sum = warp_sum(sum);
+        if (lane == 0) sc[tt] = sum;
+      }
+      __syncthreads();
+    }
+#pragma unroll 1
+    for (int tt = 0; tt < nt; ++tt) {
+      const float4 v4 = *reinterpret_cast<const float4*>(&sv[tt][col0]);
+      const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
+      const float4* r4 = reinterpret_cast<const float4*>(&sr[tt][ib * RS]);
+      const float4* k4 = reinterpret_cast<const float4*>(&sk[tt][ib * RS]);
+      const float4* w4 = reinterpret_cast<const float4*>(&sw[tt][ib * RS]);
+      float o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int q = 0; q < RI / 4; ++q) {
+        if (row0 + 4 * q < d) {
+          const float4 kq = k4[q], wq = w4[q];
+          const float kk[4] = {kq.x, kq.y, kq.z, kq.w}, ww[4] = {wq.x, wq.y, wq.z, wq.w};
+          float rr[4] = {0.f, 0.f, 0.f, 0.f};
+          if (MODE != 1) {
+            const float4 rq = r4[q];
+            rr[0] = rq.x; rr[1] = rq.y; rr[2] = rq.z; rr[3] = rq.w;
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+              if (MODE != 1) o[cc] = fmaf(rr[e], S[cc][4 * q + e], o[cc]);
+              S[cc][4 * q + e] = fmaf(ww[e], S[cc][4 * q + e], kk[e] * vv[cc]);
+            }
+        }
+      }
+      if (MODE == 1) continue;
+#pragma unroll
+      for (int m = 1; m < NIB; m <<= 1)
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) o[cc] += __shfl_xor_sync(0xffffffffu, o[cc], m);
+      if (ib == 0) {
+        const float bonus = sc[tt];
+        *reinterpret_cast<float4*>(&so[tt][col0]) = make_float4(fmaf(bonus, vv[0], o[0]), fmaf(bonus, vv[1], o[1]),
+                                                                fmaf(bonus, vv[2], o[2]), fmaf(bonus, vv[3], o[3]));
+      }
+    }
+    if (MODE == 1) continue;
+    __syncthreads();
+    // a token per warp: the head's outputs divided by their root mean square, times the norm's weight and the gate
+    for (int tt = warp; tt < nt; tt += NW) {
+      float ss = 0.f;
+      for (int i = lane; i < d; i += 32) ss += so[tt][i] * so[tt][i];
+      const float inv = rsqrtf(warp_sum(ss) / (float)d + a.eps);
+      const size_t t = (size_t)(tb + tt);
+      for (int i = lane; i < d; i += 32) ((T*)a.out)[t * hd + head * d + i] = from_f32<T>(so[tt][i] * inv * sg[tt][i]);
+    }
+  }
+  const bool store_state = MODE == 1 || t1 == q1;   // MODE 0/3: the sequence's last token of this step is here
+  if (store_state) {
+    float* dst = MODE == 1 ? cs : slot_state;
+#pragma unroll
+    for (int r = 0; r < RI; ++r) {
+      if (row0 + r < d && col0 < d) {
+        float* p = dst + (size_t)(row0 + r) * d + col0;
+        if (vec_state) {
+          *reinterpret_cast<float4*>(p) = make_float4(S[0][r], S[1][r], S[2][r], S[3][r]);
+        } else {
+          p[0] = S[0][r];
+          if (col0 + 1 < d) p[1] = S[1][r];
+          if (col0 + 2 < d) p[2] = S[2][r];
+          if (col0 + 3 < d) p[3] = S[3][r];
+        }
+      }
     }
   }
   if (MODE == 1) {
-    if (live) {
-#pragma unroll
-      for (int i = 0; i < DMAX; ++i)
-        if (i < d) cs[(size_t)i * d + j] = S[i];
-      a.chunk_decay[(((size_t)b * a.max_chunks + c) * a.heads + head) * d + j] = decay_prod;
-    }
+    if (live) a.chunk_decay[(((size_t)b * a.max_chunks + c) * a.heads + head) * d + tid] = decay_prod;
     return;
   }
-  if (t1 == q1) {   // the sequence's last token of this step is here: the state goes back to the slot
-    if (live) {
-#pragma unroll
-      for (int i = 0; i < DMAX; ++i)
-        if (i < d) slot_state[(size_t)i * d + j] = S[i];
-    }
-    if (head == 0) {
-      const T* last = (const T*)a.x + (size_t)(q1 - 1) * a.width;
-      for (int cidx = j; cidx < a.width; cidx += blockDim.x) a.prev_state[(size_t)slot * a.width + cidx] = to_f32<T>(last[cidx]);
-    }
+  if (t1 == q1 && head == 0) {
+    const T* last = (const T*)a.x + (size_t)(q1 - 1) * a.width;
+    for (int cidx = tid; cidx < a.width; cidx += blockDim.x) a.prev_state[(size_t)slot * a.width + cidx] = to_f32<T>(last[cidx]);
   }
 }
 
 // Chain the chunks: on entry chunk_state[c] holds chunk c's end state from zero (every chunk but the sequence's
 // last one); on exit it holds chunk c's true start state, chunk 0's being the slot's state.  One thread per state
-// element, chunks in order.
+// element (256 elements a block), chunks in order.
 __global__ void wkv_chain_kernel(WkvArgs a) {
   pdl_wait_block();
   pdl_launch_dependents();
   const int head = blockIdx.x, b = blockIdx.y, d = a.d;
+  const int e = blockIdx.z * blockDim.x + threadIdx.x;     // this thread's state element
+  if (e >= d * d) return;
   const int q_len = a.seq_qstart[b + 1] - a.seq_qstart[b];
   const int n_chunks = (q_len + a.chunk - 1) / a.chunk;
   const int slot = a.seq_slot[b];
   if (slot < 0 || slot >= a.n_slots) return;
-  const float* slot_state = a.state + ((size_t)slot * a.heads + head) * d * d;
-  for (int e = threadIdx.x; e < d * d; e += blockDim.x) {
-    const int i = e / d;
-    float s = slot_state[e];
-    for (int c = 0; c < n_chunks; ++c) {
-      const size_t at = ((size_t)b * a.max_chunks + c) * a.heads + head;
-      float local = 0.f, p = 0.f;
-      if (c + 1 < n_chunks) {
-        local = a.chunk_state[at * d * d + e];
-        p = a.chunk_decay[at * d + i];
+  const int i = e / d;
+  const size_t per = (size_t)a.heads * d * d, per_decay = (size_t)a.heads * d;
+  float* cs = a.chunk_state + ((size_t)b * a.max_chunks * a.heads + head) * d * d + e;       // chunk c: cs[c * per]
+  const float* cd = a.chunk_decay + ((size_t)b * a.max_chunks * a.heads + head) * d + i;      // chunk c: cd[c * per_decay]
+  float s = a.state[((size_t)slot * a.heads + head) * d * d + e];
+  // four chunks' loads in flight at a time; the last chunk of the sequence has left neither end state nor decays
+  for (int c0 = 0; c0 < n_chunks; c0 += 4) {
+    float local[4], p[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = c0 + k;
+      const bool has = c + 1 < n_chunks;
+      local[k] = has ? cs[(size_t)c * per] : 0.f;
+      p[k] = has ? cd[(size_t)c * per_decay] : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = c0 + k;
+      if (c < n_chunks) {
+        cs[(size_t)c * per] = s;          // chunk c's true start
+        s = fmaf(p[k], s, local[k]);
       }
-      a.chunk_state[at * d * d + e] = s;   // chunk c's true start
-      s = fmaf(p, s, local);
     }
   }
 }
@@ -212,15 +393,15 @@ template <typename T, int DMAX>
 static int launch_wkv(const WkvArgs& a, int max_q, cudaStream_t stream) {
   if (a.chunk > 0) {
     dim3 grid(a.heads, a.n_seqs, a.max_chunks);
-    pe::launch(wkv_scan_kernel<T, DMAX, 1>, grid, DMAX, 0, stream, a);
+    pe::launch(wkv_scan_kernel<T, DMAX, 1>, grid, WkvTile<DMAX>::NT, 0, stream, a);
     PE_LAUNCH_CHECK();
-    pe::launch(wkv_chain_kernel, dim3(a.heads, a.n_seqs), 256, 0, stream, a);
+    pe::launch(wkv_chain_kernel, dim3(a.heads, a.n_seqs, (a.d * a.d + 255) / 256), 256, 0, stream, a);
     PE_LAUNCH_CHECK();
-    pe::launch(wkv_scan_kernel<T, DMAX, 3>, grid, DMAX, 0, stream, a);
+    pe::launch(wkv_scan_kernel<T, DMAX, 3>, grid, WkvTile<DMAX>::NT, 0, stream, a);
     PE_LAUNCH_CHECK();
     return PE_OK;
   }
-  pe::launch(wkv_scan_kernel<T, DMAX, 0>, dim3(a.heads, a.n_seqs, 1), DMAX, 0, stream, a);
+  pe::launch(wkv_scan_kernel<T, DMAX, 0>, dim3(a.heads, a.n_seqs, 1), WkvTile<DMAX>::NT, 0, stream, a);
   PE_LAUNCH_CHECK();
   return PE_OK;
 }
@@ -242,6 +423,14 @@ extern "C" int pe_token_shift_mix(int dtype, const void* x, const float* mu, int
   if (n_tokens <= 0) return PE_OK;
   if (width <= 0 || n_mix <= 0) return PE_ERR_BAD_ARGUMENT;
   const int threads = width >= 1024 ? 256 : 128;
+  const bool vec8 = dtype == PE_BF16 && width % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                    (uintptr_t)mu % 16 == 0 && (uintptr_t)prev_state % 16 == 0 && ((size_t)n_tokens * width) % 8 == 0;
+  if (vec8) {
+    pe::launch(pe::token_shift_mix_vec8_kernel, n_tokens, width >= 2048 ? 256 : 128, 0, stream, (const __nv_bfloat16*)x, mu, n_mix,
+               prev_state, token_seq, seq_slot, seq_qstart, (__nv_bfloat16*)out, n_tokens, width, n_slots, status);
+    PE_LAUNCH_CHECK();
+    return PE_OK;
+  }
   if (dtype == PE_F32)
     pe::launch(pe::token_shift_mix_kernel<float>, n_tokens, threads, 0, stream, (const float*)x, mu, n_mix, prev_state, token_seq,
                seq_slot, seq_qstart, (float*)out, n_tokens, width, n_slots, status);
