@@ -71,7 +71,7 @@ def timed(torch, fn, steps, warmup, flush=None, graph=False):
 
 def model_speeds(pe, torch, cfg, prompt, batch, context, steps, warmup):
     """(prompt tokens/s, decode tokens/s, kernels per decode step) through the step function."""
-    vocab = getattr(cfg, "vocab", None) or cfg.vocab_size
+    vocab = cfg.vocab_size
     eng = pe.Engine.from_random(cfg, seed=0, dtype="bfloat16", max_context_len=context + 64,
                                 max_cache_tokens=(batch + 1) * (context + 64), max_batch=batch)
     for g in eng.cache.groups:

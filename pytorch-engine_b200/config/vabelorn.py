@@ -23,7 +23,7 @@ from .base import ConfigError, ModelConfig, require_float, require_int
 from .registry import register_preset_folder
 
 # The file gives no longest sequence; position tables are made for what the engine is asked to hold, up to this.
-MAX_POSITIONS = 1 << 20
+MAX_POSITIONS = 1 << 17
 
 
 @dataclass(frozen=True)
@@ -202,6 +202,10 @@ class VabelornConfig(ModelConfig):
     @property
     def max_positions(self) -> int:
         return MAX_POSITIONS
+
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
 
     @property
     def stop_token_ids(self) -> Tuple[int, ...]:

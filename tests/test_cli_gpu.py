@@ -66,3 +66,27 @@ def test_cli_seeded_temperature_tiny_b(pe, tmp_path, capsys):
     seed_at = argv.index("--sampling-seed") + 1
     other = _run_cli(capsys, argv[:seed_at] + ["12"] + argv[seed_at + 1:])
     assert [r["token_ids"] for r in other] != [r["token_ids"] for r in out]
+
+
+def test_cli_greedy_vabelorn(pe, tmp_path, capsys):
+    """The second architecture through the same command line: a folder written from the preset, greedy tokens in
+    float32 against the plain implementation's best token at every step."""
+    import plain_vabelorn
+    from safetensors.torch import load_file
+
+    folder = str(tmp_path / "v")
+    pe.write_random_model(folder, pe.preset("vabelorn_tiny"), 5)
+    with open(folder + "/config.json") as fh:
+        cfg = json.load(fh)
+    w = {k: v.float() for k, v in load_file(folder + "/model.safetensors").items()}
+    prompts = _prompts(cfg["vocab"], (3, 11, 70), 2)
+    argv = ["--model", folder, "--dtype", "fp32", "--ctx", "256", "--max-tokens", "6", "--temperature", "0", "--json"]
+    for p in prompts:
+        argv += ["--prompt-ids", ",".join(map(str, p))]
+    out = _run_cli(capsys, argv)
+    for r, p in zip(out, prompts):
+        assert r["completion_tokens"] == 6
+        ref = plain_vabelorn.forward(cfg, w, p + r["token_ids"])
+        for j, tok in enumerate(r["token_ids"]):
+            row = ref[len(p) - 1 + j]
+            assert float(row.max() - row[tok]) <= 1e-4 * float(ref.abs().max())
