@@ -143,44 +143,49 @@ struct WkvArgs {
 //         writes the slot's state, which no block of this launch reads
 //
 // A block holds one head's state in registers, a tile of 4 columns x RI rows per thread (the DMAX / 4 column blocks
-// times NIB row blocks are the block's threads).  It walks its tokens in batches of TB: all threads stage the batch's
-// r, k, w (the decay itself, exponentials taken here) and v in shared memory with the batch's loads in flight
-// together; then every thread runs the batch's tokens through its tile: three multiply-adds per state element and
-// token, with r, k, w of its row block read as 16-byte pieces that serve four columns each (a thread that owned a
-// whole column read twelve bytes of shared memory per state element and was bound by that), the partial outputs of
-// the row blocks added up by shuffles and left in shared memory; the per-head norm, the gate and the store are then
-// done a token per warp.  The bonus term is the same number for every column, sum_i r_i u_i k_i times v_j, so it is
-// summed once per token.  Barriers per batch, not per token.  Row blocks lie 4 floats apart from a multiple of 32 in
-// shared memory, so that the four (or eight) pieces a warp reads at once fall into different banks.
+// times NIB row blocks are the block's threads).  It walks its tokens in batches of TB.  The first DMAX threads are
+// also the stagers, one channel each: a stager holds the next batch's raw r, k, v, g and decay input in registers
+// (their loads are issued before the current batch's arithmetic, so memory latency hides behind it), and at a batch's
+// start turns them into what the arithmetic reads from shared memory: r, k, the decay itself (exponentials taken
+// here), r*u*k for the bonus term, v, and silu(g) times the norm's weight.  Then every thread runs the batch's tokens
+// through its tile: three multiply-adds per state element and token, with r, k, w of its row block read as 16-byte
+// pieces that serve four columns each (a thread that owned a whole column read twelve bytes of shared memory per
+// state element and was bound by that); the partial outputs of the row blocks, and their parts of the bonus sum
+// sum_i r_i u_i k_i (the same number for every column), are added up by shuffles and the outputs left in shared
+// memory; the per-head norm, the gate and the store are then done a token per warp.  Row blocks lie 4 floats apart
+// from a multiple of 32 in shared memory, so that the four (or eight) pieces a warp reads at once fall into different
+// banks.
 template <int DMAX> struct WkvTile {
   static constexpr int NIB = DMAX <= 128 ? 4 : 8;     // row blocks
   static constexpr int RI = DMAX / NIB;               // rows per thread
   static constexpr int NJB = DMAX / 4;                // column blocks
   static constexpr int NT = NJB * NIB;                // threads per block
-  static constexpr int TB = DMAX <= 64 ? 16 : (DMAX == 128 ? 8 : 4);   // tokens per batch (shared memory: under 48 KB, and eight blocks an SM at 64)
+  static constexpr int TB = 4;                        // tokens per batch
   static constexpr int RS = RI + 4;                   // floats from one row block to the next in shared memory
   static constexpr int ROWW = NIB * RS;
   static constexpr int MIN_BLOCKS = DMAX <= 32 ? 16 : (DMAX == 64 ? 8 : (DMAX == 128 ? 2 : 1));
 };
 
+template <typename T> __device__ __forceinline__ float silu_of(float g) { return g / (1.f + expf(-g)); }
+// a gate that is rounded to bfloat16 afterwards may take the hardware's approximate exponential and reciprocal
+template <> __device__ __forceinline__ float silu_of<__nv_bfloat16>(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+
 template <typename T, int DMAX, int MODE>
 __global__ void __launch_bounds__(WkvTile<DMAX>::NT, MODE == 0 ? 1 : WkvTile<DMAX>::MIN_BLOCKS) wkv_scan_kernel(WkvArgs a) {
   typedef WkvTile<DMAX> TL;
   constexpr int NIB = TL::NIB, RI = TL::RI, NT = TL::NT, TB = TL::TB, RS = TL::RS, NW = NT / 32;
-  __shared__ __align__(16) float sr[TB][TL::ROWW], sk[TB][TL::ROWW], sw[TB][TL::ROWW];
+  __shared__ __align__(16) float sr[TB][TL::ROWW], sk[TB][TL::ROWW], sw[TB][TL::ROWW], sb[TB][TL::ROWW];
   __shared__ __align__(16) float sv[TB][DMAX], so[TB][DMAX];
-  __shared__ float sg[MODE == 1 ? 1 : TB][DMAX];      // silu(g) times the norm's weight
-  __shared__ float sc[TB];
+  __shared__ float sg[TB][DMAX];                      // silu(g) times the norm's weight
   const int tid = threadIdx.x, d = a.d;
   const int warp = tid >> 5, lane = tid & 31;
   const int ib = tid % NIB, jb = tid / NIB;          // this thread's row block and column block
   const int head = blockIdx.x, b = blockIdx.y, c = blockIdx.z;
   const int hd = a.heads * d;
-  // as a stager, thread `tid` brings channel `tid` of the head (the first DMAX threads do)
-  const bool stager = tid < DMAX;
+  const bool stager = tid < DMAX;                    // as a stager, thread `tid` brings channel `tid` of the head
   const bool live = tid < d;
   const int col = head * d + tid;
-  const int spos = (tid / RI) * RS + (tid % RI);     // where channel `tid` lies in a row of sr, sk, sw
+  const int spos = (tid / RI) * RS + (tid % RI);     // where channel `tid` lies in a row of sr, sk, sw, sb
   float w0 = 0.f, uj = 0.f, gn = 0.f;
   if (live) {
     w0 = a.w0[col];
@@ -202,6 +207,23 @@ __global__ void __launch_bounds__(WkvTile<DMAX>::NT, MODE == 0 ? 1 : WkvTile<DMA
     if (tid == 0) report(a.status, kStatusSlotOutOfRange, b, slot, a.n_slots);
     return;
   }
+  const T* R = (const T*)a.r; const T* K = (const T*)a.k; const T* V = (const T*)a.v; const T* G = (const T*)a.g;
+  float pr[TB], pk[TB], pv[TB], pg[TB], pw[TB];      // a stager's raw inputs of the batch to come
+  auto fetch = [&](int tb) {
+#pragma unroll
+    for (int e = 0; e < TB; ++e) {
+      pr[e] = pk[e] = pv[e] = pg[e] = pw[e] = 0.f;
+      if (live && tb + e < t1) {
+        const size_t at = (size_t)(tb + e) * a.ld + col;
+        pr[e] = to_f32<T>(R[at]);
+        pk[e] = to_f32<T>(K[at]);
+        pv[e] = to_f32<T>(V[at]);
+        if (MODE != 1) pg[e] = to_f32<T>(G[at]);
+        pw[e] = a.wlin[(size_t)(tb + e) * hd + col];
+      }
+    }
+  };
+  fetch(t0);
   float* slot_state = a.state + ((size_t)slot * a.heads + head) * d * d;
   float* cs = (MODE != 0) ? a.chunk_state + (((size_t)b * a.max_chunks + c) * a.heads + head) * d * d : nullptr;
   const float* start = (MODE == 0) ? slot_state : cs;
@@ -225,54 +247,27 @@ __global__ void __launch_bounds__(WkvTile<DMAX>::NT, MODE == 0 ? 1 : WkvTile<DMA
     S[0][r] = x.x; S[1][r] = x.y; S[2][r] = x.z; S[3][r] = x.w;
   }
   float decay_prod = 1.f;   // MODE 1: stager `tid` keeps the product of its channel's decays
-  const T* R = (const T*)a.r; const T* K = (const T*)a.k; const T* V = (const T*)a.v; const T* G = (const T*)a.g;
   for (int tb = t0; tb < t1; tb += TB) {
     const int nt = min(TB, t1 - tb);
     __syncthreads();                       // the batch before this one has been read to its end
     if (stager) {
 #pragma unroll
-      for (int t4 = 0; t4 < TB; t4 += 4) {  // four tokens' loads in flight at a time
-        float rr[4], kk[4], ww[4], vv[4], gg[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int tt = t4 + e;
-          rr[e] = kk[e] = vv[e] = ww[e] = gg[e] = 0.f;
-          if (live && tt < nt) {
-            const size_t at = (size_t)(tb + tt) * a.ld + col;
-            rr[e] = to_f32<T>(R[at]);
-            kk[e] = to_f32<T>(K[at]);
-            vv[e] = to_f32<T>(V[at]);
-            if (MODE != 1) gg[e] = to_f32<T>(G[at]);
-            ww[e] = a.wlin[(size_t)(tb + tt) * hd + col];
-          }
-        }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int tt = t4 + e;
-          const float w = (live && tt < nt) ? expf(-expf(ww[e] + w0)) : 0.f;
-          sr[tt][spos] = rr[e];             // channels beyond d hold zeros: their rows of the state stay zero
-          sk[tt][spos] = kk[e];
-          sw[tt][spos] = w;
-          sv[tt][tid] = vv[e];
-          if (MODE == 1) {
-            if (live && tt < nt) decay_prod *= w;
-          } else {
-            so[tt][tid] = rr[e] * uj * kk[e];
-            sg[tt][tid] = gg[e] / (1.f + expf(-gg[e])) * gn;
-          }
+      for (int e = 0; e < TB; ++e) {
+        const float w = (live && e < nt) ? expf(-expf(pw[e] + w0)) : 0.f;
+        sr[e][spos] = pr[e];                // channels beyond d hold zeros: their rows of the state stay zero
+        sk[e][spos] = pk[e];
+        sw[e][spos] = w;
+        sv[e][tid] = pv[e];
+        if (MODE == 1) {
+          if (live && e < nt) decay_prod *= w;
+        } else {
+          sb[e][spos] = pr[e] * uj * pk[e];
+          sg[e][tid] = silu_of<T>(pg[e]) * gn;
         }
       }
     }
     __syncthreads();
-    if (MODE != 1) {                       // the bonus: one number per token
-      for (int tt = warp; tt < nt; tt += NW) {
-        float sum = 0.f;
-        for (int i = lane; i < d; i += 32) sum += so[tt][i];
-        sum = warp_sum(sum);
-        if (lane == 0) sc[tt] = sum;
-      }
-      __syncthreads();
-    }
+    if (stager) fetch(tb + TB);            // on its way while this batch is worked on
 #pragma unroll 1
     for (int tt = 0; tt < nt; ++tt) {
       const float4 v4 = *reinterpret_cast<const float4*>(&sv[tt][col0]);
@@ -280,7 +275,9 @@ __global__ void __launch_bounds__(WkvTile<DMAX>::NT, MODE == 0 ? 1 : WkvTile<DMA
       const float4* r4 = reinterpret_cast<const float4*>(&sr[tt][ib * RS]);
       const float4* k4 = reinterpret_cast<const float4*>(&sk[tt][ib * RS]);
       const float4* w4 = reinterpret_cast<const float4*>(&sw[tt][ib * RS]);
+      const float4* b4 = reinterpret_cast<const float4*>(&sb[tt][ib * RS]);
       float o[4] = {0.f, 0.f, 0.f, 0.f};
+      float bonus = 0.f;
 #pragma unroll
       for (int q = 0; q < RI / 4; ++q) {
         if (row0 + 4 * q < d) {
@@ -288,8 +285,9 @@ __global__ void __launch_bounds__(WkvTile<DMAX>::NT, MODE == 0 ? 1 : WkvTile<DMA
           const float kk[4] = {kq.x, kq.y, kq.z, kq.w}, ww[4] = {wq.x, wq.y, wq.z, wq.w};
           float rr[4] = {0.f, 0.f, 0.f, 0.f};
           if (MODE != 1) {
-            const float4 rq = r4[q];
+            const float4 rq = r4[q], bq = b4[q];
             rr[0] = rq.x; rr[1] = rq.y; rr[2] = rq.z; rr[3] = rq.w;
+            bonus += (bq.x + bq.y) + (bq.z + bq.w);
           }
 #pragma unroll
           for (int e = 0; e < 4; ++e)
@@ -302,14 +300,14 @@ __global__ void __launch_bounds__(WkvTile<DMAX>::NT, MODE == 0 ? 1 : WkvTile<DMA
       }
       if (MODE == 1) continue;
 #pragma unroll
-      for (int m = 1; m < NIB; m <<= 1)
+      for (int m = 1; m < NIB; m <<= 1) {
+        bonus += __shfl_xor_sync(0xffffffffu, bonus, m);
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) o[cc] += __shfl_xor_sync(0xffffffffu, o[cc], m);
-      if (ib == 0) {
-        const float bonus = sc[tt];
+      }
+      if (ib == 0)
         *reinterpret_cast<float4*>(&so[tt][col0]) = make_float4(fmaf(bonus, vv[0], o[0]), fmaf(bonus, vv[1], o[1]),
                                                                 fmaf(bonus, vv[2], o[2]), fmaf(bonus, vv[3], o[3]));
-      }
     }
     if (MODE == 1) continue;
     __syncthreads();
