@@ -393,7 +393,7 @@ def _wkv_plain(r, k, v, gl, wlin, w0, u, gn, H, d, eps, S):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,d", [(3, 24), (2, 64), (1, 128), (2, 33)])
+@pytest.mark.parametrize("H,d", [(3, 24), (2, 64), (1, 128), (2, 33), (1, 160), (2, 6)])
 def test_recurrence_whole_chunked_and_token_by_token(pe, dtype, H, d):
     """Three sequences of unequal lengths, one of them continuing from a state: in one go, cut into chunks of 16 and of
     64, and one token at a time; every way against the plain recurrence, and the states they leave against each other."""
