@@ -342,9 +342,13 @@ __global__ void __launch_bounds__(WkvTile<DMAX>::NT, MODE == 0 ? 1 : WkvTile<DMA
     if (live) a.chunk_decay[(((size_t)b * a.max_chunks + c) * a.heads + head) * d + tid] = decay_prod;
     return;
   }
-  if (t1 == q1 && head == 0) {
+  if (t1 == q1) {
+    // the sequence's last input row becomes `prev`; each head's block copies its share of the width (one block
+    // copying all of it, 64 threads wide, was the longest thing a decode step's launch of this kernel did)
     const T* last = (const T*)a.x + (size_t)(q1 - 1) * a.width;
-    for (int cidx = tid; cidx < a.width; cidx += blockDim.x) a.prev_state[(size_t)slot * a.width + cidx] = to_f32<T>(last[cidx]);
+    const int per = (a.width + a.heads - 1) / a.heads;
+    const int hi = min(a.width, (head + 1) * per);
+    for (int cidx = head * per + tid; cidx < hi; cidx += blockDim.x) a.prev_state[(size_t)slot * a.width + cidx] = to_f32<T>(last[cidx]);
   }
 }
 
