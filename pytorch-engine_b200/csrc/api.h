@@ -63,6 +63,8 @@ int pe_embed_gather(int dtype, const void* table, const int* ids, float* out, in
 int pe_gemm_smallm_supported(int M, int N, int K);
 int pe_gemm_smallm(const void* x, long long ldx, const void* w, void* y, long long ldy, int M, int N, int K,
     int out_f32, int pair_offset, int n_sms, cudaStream_t stream);
+int pe_gemm_smallm_grouped(const void* x, long long ldx, long long x_group_stride, int groups, int group_rows,
+    const void* w, void* y, long long ldy, int M, int K, int out_f32, int n_sms, cudaStream_t stream);
 
 // gemm_umma.cu
 int pe_gemm_umma_supported(int M, int N, int K, int pair_offset);

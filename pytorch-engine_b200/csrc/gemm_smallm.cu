@@ -29,6 +29,10 @@ struct Args {
   void* y; long long ldy;
   int M, N, K;
   int pair_offset;             // PAIR: row n is combined with row n + pair_offset; N counts output columns
+  // Grouped form: the weight rows are several matrices stacked, `group_rows` rows each (a multiple of 16), and the
+  // rows of matrix i multiply an input of their own, x + i * x_group_stride: several projections of several inputs
+  // in one launch.  0: one input for all rows.
+  int group_rows; long long x_group_stride;
 };
 
 __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
@@ -87,7 +91,8 @@ __global__ void __launch_bounds__(WARPS * 32, NT == 1 ? 16 / WARPS : 1) gemm_sma
   for (int n = 0; n < NT; ++n) {
     const int m = n * 8 + g;
     x_ok[n] = m < a.M;
-    xr[n] = reinterpret_cast<const uint4*>(a.x + (size_t)(x_ok[n] ? m : 0) * a.ldx) + t;
+    const __nv_bfloat16* xg = a.x + (a.group_rows > 0 ? (size_t)(n0 / a.group_rows) * a.x_group_stride : 0);
+    xr[n] = reinterpret_cast<const uint4*>(xg + (size_t)(x_ok[n] ? m : 0) * a.ldx) + t;
   }
   float c[(PAIR ? 2 : 1) * NT][4];
 #pragma unroll
@@ -237,6 +242,7 @@ extern "C" int pe_gemm_smallm(const void* x, long long ldx, const void* w, void*
   pe::smallm::Args a;
   a.x = (const __nv_bfloat16*)x; a.ldx = ldx; a.w = (const __nv_bfloat16*)w; a.y = y; a.ldy = ldy;
   a.M = M; a.N = N; a.K = K; a.pair_offset = pair_offset;
+  a.group_rows = 0; a.x_group_stride = 0;
   using namespace pe::smallm;
   if (n_sms <= 0) n_sms = pe::kSMs;
   const bool pair = pair_offset > 0;
@@ -245,5 +251,26 @@ extern "C" int pe_gemm_smallm(const void* x, long long ldx, const void* w, void*
     return out_f32 ? launch<1, false, float>(a, n_sms, stream) : launch<1, false, __nv_bfloat16>(a, n_sms, stream);
   }
   if (pair) return out_f32 ? launch<2, true, float>(a, n_sms, stream) : launch<2, true, __nv_bfloat16>(a, n_sms, stream);
+  return out_f32 ? launch<2, false, float>(a, n_sms, stream) : launch<2, false, __nv_bfloat16>(a, n_sms, stream);
+}
+
+// Several projections of several inputs in one launch: w holds `groups` matrices of `group_rows` rows stacked
+// ([groups * group_rows, K]); the rows of matrix i multiply x + i * x_group_stride ([M, K], row stride ldx); y is
+// [M, groups * group_rows], matrix i's results in columns [i * group_rows, (i + 1) * group_rows).
+extern "C" int pe_gemm_smallm_grouped(const void* x, long long ldx, long long x_group_stride, int groups, int group_rows,
+                                      const void* w, void* y, long long ldy, int M, int K, int out_f32, int n_sms,
+                                      cudaStream_t stream) {
+  if (M <= 0 || groups <= 0) return PE_OK;
+  if (group_rows <= 0 || group_rows % 16) return PE_ERR_UNSUPPORTED_SIZE;
+  const int N = groups * group_rows;
+  if (!pe_gemm_smallm_supported(M, N, K)) return PE_ERR_UNSUPPORTED_SIZE;
+  if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || (ldx * 2) % 16 || (x_group_stride * 2) % 16) return PE_ERR_BAD_ARGUMENT;
+  pe::smallm::Args a;
+  a.x = (const __nv_bfloat16*)x; a.ldx = ldx; a.w = (const __nv_bfloat16*)w; a.y = y; a.ldy = ldy;
+  a.M = M; a.N = N; a.K = K; a.pair_offset = 0;
+  a.group_rows = group_rows; a.x_group_stride = x_group_stride;
+  using namespace pe::smallm;
+  if (n_sms <= 0) n_sms = pe::kSMs;
+  if (M <= 8) return out_f32 ? launch<1, false, float>(a, n_sms, stream) : launch<1, false, __nv_bfloat16>(a, n_sms, stream);
   return out_f32 ? launch<2, false, float>(a, n_sms, stream) : launch<2, false, __nv_bfloat16>(a, n_sms, stream);
 }

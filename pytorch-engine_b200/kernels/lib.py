@@ -51,6 +51,7 @@ _SIGNATURES = {
     "pe_attention_mma_supported": [I, I, I],
     "pe_gemm_smallm": [P, L, P, P, L, I, I, I, I, I, I, P],
     "pe_gemm_smallm_supported": [I, I, I],
+    "pe_gemm_smallm_grouped": [P, L, L, I, I, P, P, L, I, I, I, I, P],
     "pe_gemm_umma": [P, L, P, P, L, I, I, I, I, I, I, P, P],
     "pe_gemm_umma_supported": [I, I, I, I],
     "pe_gemm_umma2": [P, L, P, P, L, I, I, I, I, I, I, P, P],

@@ -333,6 +333,27 @@ def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, pair_o
     _count(1)
 
 
+def gemm_smallm_grouped_supported(xs: torch.Tensor, weight: torch.Tensor, group_rows: int) -> bool:
+    """Whether csrc/gemm_smallm.cu takes ``xs [G, M, K]`` times ``weight [G * group_rows, K]`` in one launch."""
+    return (xs.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and xs.dim() == 3 and xs.is_contiguous()
+            and weight.is_contiguous() and xs.shape[1] <= 16 and xs.shape[2] % 8 == 0 and group_rows % 16 == 0
+            and weight.shape[0] == xs.shape[0] * group_rows and weight.shape[1] == xs.shape[2]
+            and xs.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and (xs.shape[1] * xs.shape[2]) % 8 == 0)
+
+
+def gemm_smallm_grouped(xs: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, group_rows: int) -> None:
+    """``out[:, i * group_rows : (i + 1) * group_rows] = xs[i] @ weight[i * group_rows : (i + 1) * group_rows]^T`` for every
+    i, in one launch: several projections, each of an input of its own (bfloat16, at most 16 rows)."""
+    _need(gemm_smallm_grouped_supported(xs, weight, group_rows), "gemm_smallm_grouped: shapes, dtypes or alignment")
+    g, m, k = xs.shape
+    _need(out.shape[0] == m and out.shape[1] == g * group_rows and out.stride(-1) == 1
+          and out.dtype in (torch.bfloat16, torch.float32), "gemm_smallm_grouped: out [M, G * group_rows]")
+    check(library().pe_gemm_smallm_grouped(_ptr(xs), k, m * k, g, group_rows, _ptr(weight), _ptr(out), out.stride(0), m, k,
+                                           1 if out.dtype == torch.float32 else 0, sm_count(xs.device), _stream()),
+          "gemm_smallm_grouped")
+    _count(1)
+
+
 _SM_COUNT = {}
 
 

@@ -159,7 +159,22 @@ class Runtime:
         h.start(n)
         return h
 
-    # ---- matrix product ----------------------------------------------------------------------
+    # ---- matrix products ---------------------------------------------------------------------
+    def batched_linear(self, xs: torch.Tensor, weights: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """``out[i] = xs[i] @ weights[i]^T`` for ``xs [G, M, K]``, ``weights [G, N, K]``: several projections, each of an
+        input of its own, as one library call (float32: true float32; bfloat16: float32 accumulation)."""
+        if not self.is_cuda:
+            raise KernelError("this package computes on a CUDA device only; there is no CPU path")
+        tf32 = torch.backends.cuda.matmul.allow_tf32
+        red = torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction
+        torch.backends.cuda.matmul.allow_tf32 = False
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+        try:
+            return torch.bmm(xs, weights.transpose(1, 2), out=out)
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = tf32
+            torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = red
+
     def linear(self, x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """``x [M, K] @ weight [N, K]^T -> [M, N]``."""

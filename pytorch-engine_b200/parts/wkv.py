@@ -70,7 +70,8 @@ class WkvMixer:
         self.inner = self.n_heads * self.head_dim
         f32 = torch.float32
         self.mu = torch.stack([weights[f"mu_{s}"].to(device=runtime.device, dtype=f32) for s in MIXES]).contiguous()
-        self.proj = [runtime.adopt(weights[f"{s}_proj"]) for s in "rkvg"]
+        # r, k, v, g stacked: one grouped launch for a handful of rows, one batched product otherwise
+        self.proj = torch.stack([weights[f"{s}_proj"].to(device=runtime.device, dtype=runtime.dtype) for s in "rkvg"]).contiguous()
         self.w1 = runtime.adopt(weights["w1"])
         self.w2 = runtime.adopt(weights["w2"])
         if self.w1.shape[0] != self.w2.shape[1]:
@@ -81,6 +82,25 @@ class WkvMixer:
         self.gnorm = runtime.adopt(weights["gnorm"], f32)
         self.o_proj = runtime.adopt(weights["o_proj"])
 
+    def project(self, mixes: torch.Tensor, n: int, ctx):
+        """r, k, v, g (views with one row stride) from the first four mixes: each mix times its own matrix."""
+        rt = self.runtime
+        stacked = self.proj.view(4 * self.inner, self.hidden)
+        xs = mixes[:4]
+        if (rt.gemm_backend is None and rt.own_small_gemm and n <= rt.small_gemm_rows
+                and ops.gemm_smallm_grouped_supported(xs, stacked, self.inner)):
+            out = ctx.buffer("wkv.rkvg", (n, 4 * self.inner), rt.dtype)
+            ops.gemm_smallm_grouped(xs, stacked, out, self.inner)
+            return [out[:, i * self.inner:(i + 1) * self.inner] for i in range(4)]
+        if rt.gemm_backend is None:
+            out = ctx.buffer("wkv.rkvg", (4, n, self.inner), rt.dtype)
+            rt.batched_linear(xs, self.proj, out)
+            return [out[i] for i in range(4)]
+        outs = [ctx.buffer(f"wkv.{s}", (n, self.inner), rt.dtype) for s in "rkvg"]
+        for i in range(4):
+            rt.linear(mixes[i], self.proj[i], out=outs[i])
+        return outs
+
     def forward(self, x: torch.Tensor, ctx, view, writes_cache: bool = True) -> torch.Tensor:
         if not writes_cache:
             raise ValueError("a wkv mixer folds every token into its state; it cannot run without writing it")
@@ -89,9 +109,7 @@ class WkvMixer:
         prev, state = view.state("prev"), view.state("S")
         mixes = ctx.buffer("wkv.mixes", (len(MIXES), n, self.hidden), rt.dtype)
         ops.token_shift_mix(x, self.mu, prev, ctx.token_seq, ctx.seq_slot, ctx.seq_qstart, mixes, rt.status)
-        rkvg = [ctx.buffer(f"wkv.{s}", (n, self.inner), rt.dtype) for s in "rkvg"]
-        for i in range(4):
-            rt.linear(mixes[i], self.proj[i], out=rkvg[i])
+        rkvg = self.project(mixes, n, ctx)
         low = ctx.buffer("wkv.low", (n, self.rank), rt.dtype)
         rt.linear(mixes[4], self.w1, out=low)
         ops.tanh_(low)

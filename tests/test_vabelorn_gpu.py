@@ -490,6 +490,22 @@ def test_norm_then_add_and_token_gate(pe, dtype):
     assert (out.double().cpu() - want).abs().max() < (1e-6 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.parametrize("m", [1, 5, 8, 13])
+def test_grouped_product_of_several_inputs(pe, m):
+    """Four projections, each of an input of its own, in one launch of the weight-streaming kernel."""
+    ops = pe.kernels.ops
+    g = torch.Generator().manual_seed(m)
+    G, R, K = 4, 48, 72
+    xs = torch.randn(G, m, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(G * R, K, generator=g) / 8).to(torch.bfloat16)
+    assert ops.gemm_smallm_grouped_supported(xs.to(DEV), w.to(DEV), R)
+    for dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((m, G * R), float("nan"), dtype=dtype, device=DEV)
+        ops.gemm_smallm_grouped(xs.to(DEV), w.to(DEV), out, R)
+        want = torch.cat([xs[i].double() @ w[i * R:(i + 1) * R].double().T for i in range(G)], dim=1)
+        assert (out.double().cpu() - want).abs().max() < (2e-2 if dtype == torch.bfloat16 else 1e-4)
+
+
 # ---- whole models -----------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("key", ["P", "Q", "R"])
