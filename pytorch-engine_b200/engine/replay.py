@@ -78,6 +78,31 @@ class TraceReplayer:
         return 0
 
 
+def state_bytes_per_slot(cfg) -> int:
+    """Bytes of fixed-size state that one live sequence holds, summed over the model's mixers."""
+    import math
+
+    import torch
+
+    from ..config.registry import architecture
+    from ..parts.registry import lookup
+
+    plan = architecture(cfg.architecture).plan(cfg)
+    total = 0
+    for run in plan.order:
+        if not run.writes_cache:
+            continue
+        block = plan.blocks[run.block]
+        for name in block.mixer_names():
+            spec = block.part(name)
+            cls = lookup("mixer", spec.kind)
+            req = cls.cache_request(spec.params) if hasattr(cls, "cache_request") else None
+            if req is not None and req.kind == "state":
+                for _, shape, dtype_name in req.state_shapes:
+                    total += math.prod(shape) * torch.empty((), dtype=getattr(torch, dtype_name)).element_size()
+    return total
+
+
 def main(argv=None) -> int:
     import argparse
 
@@ -97,6 +122,10 @@ def main(argv=None) -> int:
     # and one slot for each of up to 1,024 requests.
     n = max(args.max_tokens, 1)
     requests = min(n, 1024)
+    # a model whose mixers keep fixed-size state pays for every slot: no more slots than 8 GiB of state (but 64)
+    per_slot = state_bytes_per_slot(cfg)
+    if per_slot:
+        requests = max(min(requests, 64), min(requests, (8 << 30) // per_slot))
     cache_tokens = (pages_for(n) + requests) * PAGE_TOKENS
     engine = Engine(args.model, dtype=args.dtype, max_context_len=min(cfg.max_positions, pages_for(n) * PAGE_TOKENS),
                     max_cache_tokens=cache_tokens, max_slots=requests)
