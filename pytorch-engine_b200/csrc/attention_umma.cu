@@ -1,5 +1,5 @@
 // Prefill attention on the fifth-generation tensor cores (tcgen05.mma), for bfloat16, head size 128
-// and groups of up to 32 query heads per kv head.  Same contract and formulas as
+// and groups of up to 32 query heads per kv head.  Same interface and formulas as
 // attention_mma.cu (pygguf_engine/kv_cache.py:833, 2189-2192 masks; 756 head mapping; 836-861 online
 // softmax); other shapes keep using that file.
 //

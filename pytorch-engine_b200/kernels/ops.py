@@ -294,7 +294,7 @@ def attention_mma(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: int,
                   k_pages: torch.Tensor, v_pages: torch.Tensor, scratch: Optional[torch.Tensor], split_keys: int,
                   max_splits: int, status: torch.Tensor, min_range_keys: int = 0, sink: bool = False,
                   out_cos: Optional[torch.Tensor] = None, out_sin: Optional[torch.Tensor] = None) -> None:
-    """Same contract as ``attention_generic``, bfloat16 only, head sizes 64 and 128, groups up to 16.
+    """Same interface as ``attention_generic``, bfloat16 only, head sizes 64 and 128, groups up to 16.
     With ``split_keys`` 0 a sequence's keys are shared out evenly over ``max_splits`` ranges of whole pages,
     each of at least ``min_range_keys`` keys.  ``sink``: one added to the softmax's denominator.  ``out_cos,
     out_sin`` (float32 ``[rows, head_dim / 2]``): each head's output is turned back by the angle of the query's

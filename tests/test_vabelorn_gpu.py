@@ -267,7 +267,7 @@ def test_attention_with_values_of_their_own_size_against_the_formula(pe, dtype):
                 row += 1
 
 
-@pytest.mark.parametrize("d,nh,nkv", [(64, 8, 2), (128, 4, 2), (128, 6, 1)])
+@pytest.mark.parametrize("d,nh,nkv", [(64, 8, 2), (128, 4, 2), (128, 6, 1), (128, 6, 2), (128, 5, 1), (64, 16, 1), (64, 3, 3)])
 def test_tensor_core_attention_with_sink_and_turned_outputs(pe, d, nh, nkv):
     """The mma.sync kernels (prompt and single token) and the tcgen05 prompt kernel with a sink and outputs turned back,
     against the float32-arithmetic kernel on the same bfloat16 cache; one key far back stands out for every query."""
@@ -586,6 +586,29 @@ def test_unequal_batches_on_slots_used_again(pe, models, key, dtype):
             models.check(key, dtype, seqs[i], rows, range(p - 1, p + dec), f"{key} batch {batch} request {i}")
         eng.cache.check()
     assert seen[0] == seen[1]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["P", "R"])
+def test_a_decode_batch_of_twelve(pe, models, key, dtype):
+    """More sequences than the weight-streaming products take: the library products (one batched call for the
+    recurrence's four projections) inside the captured decode step."""
+    eng = models.engine(key, dtype, max_batch=12)
+    vocab = CONFIGS[key]["vocab"]
+    seqs = [_tokens(vocab, 3 + i + 6, 300 + i) for i in range(12)]
+    slots = [eng.alloc_slot() for _ in seqs]
+    got = {i: [] for i in range(12)}
+    out = eng.step([_entry(pe, s, q[:3 + i], [2 + i]) for i, (s, q) in enumerate(zip(slots, seqs))]).clone()
+    for i in range(12):
+        got[i].append(out[i:i + 1])
+    for step in range(6):
+        out = eng.step([_entry(pe, s, [q[3 + i + step]], [0]) for i, (s, q) in enumerate(zip(slots, seqs))]).clone()
+        for i in range(12):
+            got[i].append(out[i:i + 1])
+    for s in slots:
+        eng.free_slot(s)
+    for i in (0, 5, 11):
+        models.check(key, dtype, seqs[i], torch.cat(got[i]), range(2 + i, 9 + i), f"{key} request {i} of twelve")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
