@@ -268,6 +268,7 @@ __global__ void __launch_bounds__(WkvTile<DMAX>::NT, MODE == 0 ? 1 : WkvTile<DMA
     }
     __syncthreads();
     if (stager) fetch(tb + TB);            // on its way while this batch is worked on
+    asm volatile("" ::: "memory");         // the compiler may not sink these loads below the arithmetic, to where they are used
 #pragma unroll 1
     for (int tt = 0; tt < nt; ++tt) {
       const float4 v4 = *reinterpret_cast<const float4*>(&sv[tt][col0]);
