@@ -5,9 +5,10 @@ from .registry import (Architecture, architecture, architecture_names, architect
                        unregister_preset_folder)
 from .qwen3 import Qwen3Config
 from .vabelorn import VabelornConfig
+from .lunadra import LunadraConfig
 
 __all__ = [
     "ConfigError", "ModelConfig", "read_config_dict", "Architecture", "architecture", "architecture_names",
-    "architecture_of", "load_config", "register_architecture", "unregister_architecture", "Qwen3Config", "VabelornConfig",
+    "architecture_of", "load_config", "register_architecture", "unregister_architecture", "Qwen3Config", "VabelornConfig", "LunadraConfig",
     "preset", "preset_names", "register_preset_folder", "unregister_preset_folder",
 ]

@@ -131,6 +131,41 @@ int pe_wkv_recurrence(int dtype, const void* r, const void* k, const void* v, co
     float* prev_state, const void* x, int width, const int* seq_slot, const int* seq_qstart, int n_seqs, int max_q,
     int heads, int d, int n_slots, int chunk, int max_chunks, float* scratch, int* status, cudaStream_t stream);
 
+// embedding.cu (pair embedding), rmsnorm.cu (sum of scaled deltas)
+int pe_embed_pair_gather(int dtype, const void* table, const void* pairs, const int* ids, const int* token_seq,
+    const int* token_pos, const int* seq_slot, const int* seq_qstart, int* last, float* out, int n_tokens, int hidden,
+    int vocab, int buckets, int mul_prev, int mul_cur, int n_slots, int* status, cudaStream_t stream);
+int pe_rmsnorm_residual_sum(int dtype, float* residual, const void* const* deltas, const float* scales, int n_deltas,
+    const float* weight, void* out, const int* rows, int n_rows, int dim, float eps, cudaStream_t stream);
+
+// mlstm.cu
+int pe_mlstm_recurrence(int dtype, const void* q, const void* k, const void* v, const void* g, long long ld,
+    const float* gates, const float* gate_bias, const float* norm_w, float cap, float eps, float q_scale, void* out,
+    float* S, float* n, float* m, const int* seq_slot, const int* seq_qstart, int n_seqs, int heads, int d, int dv,
+    int n_slots, int* status, cudaStream_t stream);
+
+// delta_rule.cu
+int pe_short_conv_silu(int dtype, const void* x, long long ld, int col0, const float* w, int taps, float* tail,
+    const int* token_seq, const int* seq_slot, const int* seq_qstart, void* out, int n_tokens, int n_seqs, int channels,
+    int n_slots, int* status, cudaStream_t stream);
+int pe_delta_rule_recurrence(int dtype, const void* qkv, const float* a, const float* dt_bias, const float* A_log,
+    const float* b, const void* gate, long long gate_ld, const float* norm_w, float eps, float q_scale, void* out, float* S,
+    const int* seq_slot, const int* seq_qstart, int n_seqs, int heads, int kv_heads, int d, int dv, int n_slots,
+    int* status, cudaStream_t stream);
+
+// moe.cu
+int pe_moe_route(const float* logits, const float* correction, int n_tokens, int n_all, int top, int* chosen,
+    float* weight, cudaStream_t stream);
+int pe_moe_group(const int* chosen, int n_tokens, int top, int n_real, int* offsets, int* row_token, int* pair_row,
+    cudaStream_t stream);
+int pe_moe_rows_gemm(int dtype, int out_dtype, const void* x, long long x_ld, const int* row_map, const int* offsets,
+    int n_groups, int max_rows, const void* w, long long w_group_stride, void* out, long long out_ld, int n_out, int k_dim,
+    int glu, float limit, float alpha, cudaStream_t stream);
+int pe_moe_combine(int dtype, const void* rows, const void* x, const void* shared, const int* pair_row,
+    const float* weight, int top, void* out, int n_tokens, int width, cudaStream_t stream);
+int pe_glu_act(int dtype, const void* gate_up, void* out, int n_rows, int inter, int kind, float limit, float alpha,
+    cudaStream_t stream);
+
 // wait_probe.cu
 int pe_wait_probe(unsigned long long* out, int polls, cudaStream_t stream);
 long long pe_wait_limit_polls();

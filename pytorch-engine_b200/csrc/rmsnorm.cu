@@ -191,6 +191,44 @@ __global__ void __launch_bounds__(1024) rmsnorm_add_vec4_kernel(float* __restric
   }
 }
 
+// The add of several scaled sublayer outputs at once, then the norm (a block whose sublayers all read one norm's
+// output and are added together):  h = residual[row] + sum_i scale_i * delta_i[row];  out = h * rsqrt(mean(h^2) + eps) * w.
+// Modes as above: without `rows` the sum is written back to the stream, with `rows` nothing is.
+struct DeltaList {
+  const void* ptr[4];
+  float scale[4];
+  int count;
+};
+
+template <typename TDelta, typename TOut>
+__global__ void rmsnorm_sum_kernel(float* __restrict__ residual, DeltaList deltas, const float* __restrict__ weight,
+                                   TOut* __restrict__ out, const int* rows, int n_rows, int dim, float eps) {
+  extern __shared__ float row_buf[];  // dim floats
+  __shared__ float red[32];
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  if (r >= n_rows) return;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  float* res_row = residual + src * dim;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    float add = 0.f;
+    for (int i = 0; i < deltas.count; ++i)
+      add = fmaf(deltas.scale[i], to_f32<TDelta>(((const TDelta*)deltas.ptr[i])[src * dim + c]), add);
+    const float h = res_row[c] + add;
+    row_buf[c] = h;
+    ss += h * h;
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)dim + eps);
+  const bool write_back = rows == nullptr;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    const float h = row_buf[c];
+    if (write_back) res_row[c] = h;
+    if (out) out[(size_t)r * dim + c] = from_f32<TOut>(h * inv * weight[c]);
+  }
+}
+
 template <typename K>
 static int set_smem(K kernel, size_t bytes) {
   if (bytes > 48 * 1024) {
@@ -273,6 +311,36 @@ extern "C" int pe_rmsnorm_add(int dtype, float* stream, const void* delta, const
     auto k = vec ? pe::rmsnorm_add_vec4_kernel<__nv_bfloat16> : pe::rmsnorm_add_kernel<__nv_bfloat16>;
     if ((e = pe::set_smem(k, smem))) return e;
     pe::launch(k, n_rows, threads, smem, stream_, stream, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)cast, n_rows, dim, eps);
+  } else {
+    return PE_ERR_UNSUPPORTED_DTYPE;
+  }
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}
+
+extern "C" int pe_rmsnorm_residual_sum(int dtype, float* residual, const void* const* deltas, const float* scales, int n_deltas,
+                                       const float* weight, void* out, const int* rows, int n_rows, int dim, float eps,
+                                       cudaStream_t stream) {
+  if (n_rows <= 0) return PE_OK;
+  if (dim <= 0 || n_deltas < 0 || n_deltas > 4) return PE_ERR_BAD_ARGUMENT;
+  const size_t smem = (size_t)dim * sizeof(float);
+  if (smem > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;
+  pe::DeltaList list;
+  list.count = n_deltas;
+  for (int i = 0; i < 4; ++i) {
+    list.ptr[i] = i < n_deltas ? deltas[i] : nullptr;
+    list.scale[i] = i < n_deltas ? scales[i] : 0.f;
+  }
+  const int threads = dim >= 4096 ? 1024 : (dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128));
+  int e;
+  if (dtype == PE_F32) {
+    auto k = pe::rmsnorm_sum_kernel<float, float>;
+    if ((e = pe::set_smem(k, smem))) return e;
+    pe::launch(k, n_rows, threads, smem, stream, residual, list, weight, (float*)out, rows, n_rows, dim, eps);
+  } else if (dtype == PE_BF16) {
+    auto k = pe::rmsnorm_sum_kernel<__nv_bfloat16, __nv_bfloat16>;
+    if ((e = pe::set_smem(k, smem))) return e;
+    pe::launch(k, n_rows, threads, smem, stream, residual, list, weight, (__nv_bfloat16*)out, rows, n_rows, dim, eps);
   } else {
     return PE_ERR_UNSUPPORTED_DTYPE;
   }

@@ -60,9 +60,15 @@ class DecoderModel:
         ``(entry, mixer name)`` for a block with several."""
         return entry if len(block_spec.mixer_names()) <= 1 else (entry, mixer_name)
 
+    # the cache key of what the embedding keeps per sequence (an embedding of token pairs keeps the last token)
+    EMBEDDING_KEY = (-1, "embedding")
+
     def cache_requests(self) -> Dict[object, Optional[CacheRequest]]:
         """Cache key -> what the mixer that writes it needs."""
         reqs: Dict[object, Optional[CacheRequest]] = {}
+        emb = lookup("embedding", self.plan.embedding.kind)
+        if hasattr(emb, "cache_request"):
+            reqs[self.EMBEDDING_KEY] = emb.cache_request(self.plan.embedding.params)
         written = set()
         for run in self.plan.order:
             if not run.writes_cache or run.cache_entry in written:
@@ -94,7 +100,10 @@ class DecoderModel:
         """Run the step described by ``ctx``; returns float32 logits ``[n_want, vocab]``."""
         rt = self.runtime
         stream = ctx.buffer("model.stream", (ctx.n_tokens, self.hidden), torch.float32)
-        self.embedding.forward(ctx.tokens, stream)
+        if hasattr(self.embedding, "cache_request"):
+            self.embedding.forward(ctx.tokens, stream, ctx, cache.view(self.EMBEDDING_KEY))
+        else:
+            self.embedding.forward(ctx.tokens, stream)
         ctx.stream_copy = None    # a copy of the stream in the run dtype, if a block has left one (post-norm blocks do)
         pending = None
         for run in self.plan.order:

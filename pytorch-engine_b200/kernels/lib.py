@@ -74,6 +74,16 @@ _SIGNATURES = {
     "pe_attention_mma_ex": [I, P, L, P, L, I, I, I, I, I, F, I, I, P, P, I, P, P, P, P, I, I, P, P, P, I, I, I, P, P],
     "pe_attention_umma_prefill_ex": [P, L, L, P, L, I, I, I, I, I, F, I, I, P, P, I, P, P, P, P, I, I, P, P, I, P, P, P],
     "pe_attention_decode_noalloc": [I, P, L, P, L, I, I, I, I, F, I, P, P, P, P, I, I, P, P, I, I, P, P],
+    "pe_embed_pair_gather": [I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
+    "pe_rmsnorm_residual_sum": [I, P, P, P, I, P, P, P, I, I, F, P],
+    "pe_mlstm_recurrence": [I, P, P, P, P, L, P, P, P, F, F, F, P, P, P, P, P, P, I, I, I, I, I, P, P],
+    "pe_short_conv_silu": [I, P, L, I, P, I, P, P, P, P, P, I, I, I, I, P, P],
+    "pe_delta_rule_recurrence": [I, P, P, P, P, P, P, L, P, F, F, P, P, P, P, I, I, I, I, I, I, P, P],
+    "pe_moe_route": [P, P, I, I, I, P, P, P],
+    "pe_moe_group": [P, I, I, I, P, P, P, P],
+    "pe_moe_rows_gemm": [I, I, P, L, P, P, I, I, P, L, P, L, I, I, I, F, F, P],
+    "pe_moe_combine": [I, P, P, P, P, P, I, P, I, I, P],
+    "pe_glu_act": [I, P, P, I, I, I, F, F, P],
 }
 _RESTYPES = {"pe_wait_limit_polls": (L, []),
              "pe_attention_generic_scratch_floats": (L, [I, I, I, I]),

@@ -553,3 +553,140 @@ def wait_poll_seconds(device, polls: int = 20000) -> float:
 def wait_limit_seconds(device) -> float:
     """The longest that a bounded wait inside a kernel of this library lasts before it gives up."""
     return int(library().pe_wait_limit_polls()) * wait_poll_seconds(device)
+
+
+# ---- pair embedding, sum of scaled deltas -------------------------------------------------------------------------
+def embed_pair_gather(table: torch.Tensor, pairs: torch.Tensor, ids: torch.Tensor, token_seq: torch.Tensor,
+                      token_pos: torch.Tensor, seq_slot: torch.Tensor, seq_qstart: torch.Tensor, last: torch.Tensor,
+                      out: torch.Tensor, buckets: int, mul_prev: int, mul_cur: int, status: torch.Tensor) -> None:
+    """``out[t] = table[tok] + pairs[(prev * mul_prev + tok * mul_cur) % buckets]`` (row ``buckets`` at position 0);
+    ``last [slots]`` int32 holds every sequence's last token between steps (csrc/embedding.cu)."""
+    _need(ids.dtype == torch.int32 and out.dtype == torch.float32 and last.dtype == torch.int32, "embed_pair_gather: dtypes")
+    _need(table.is_contiguous() and pairs.is_contiguous() and out.is_contiguous() and last.is_contiguous(),
+          "embed_pair_gather: contiguous tensors")
+    _need(pairs.dtype == table.dtype and pairs.shape == (buckets + 1, table.shape[1]), "embed_pair_gather: pair table shape")
+    n, hidden = out.shape
+    check(library().pe_embed_pair_gather(dtype_tag(table.dtype), _ptr(table), _ptr(pairs), _ptr(ids), _ptr(token_seq),
+                                         _ptr(token_pos), _ptr(seq_slot), _ptr(seq_qstart), _ptr(last), _ptr(out), n, hidden,
+                                         table.shape[0], int(buckets), int(mul_prev), int(mul_cur), last.numel(),
+                                         _ptr(status), _stream()), "embed_pair_gather")
+    _count(1)
+
+
+def rmsnorm_residual_sum(residual: torch.Tensor, deltas, scales, weight: torch.Tensor, out: Optional[torch.Tensor], eps: float,
+                         rows: Optional[torch.Tensor] = None) -> None:
+    """``h = residual + sum_i scales[i] * deltas[i]``; ``out = rmsnorm(h) * weight`` (``out`` None: the add alone).
+    Without ``rows`` the sum is written back to the stream; with ``rows`` only those rows are read and nothing is."""
+    import ctypes
+    _need(residual.dtype == torch.float32 and weight.dtype == torch.float32 and residual.is_contiguous(), "rmsnorm_sum: stream f32")
+    _need(0 <= len(deltas) <= 4 and len(deltas) == len(scales), "rmsnorm_sum: at most four deltas, a scale for each")
+    dt = out.dtype if out is not None else (deltas[0].dtype if deltas else torch.float32)
+    for d in deltas:
+        _need(d.dtype == dt and d.is_contiguous() and d.shape == residual.shape, "rmsnorm_sum: deltas like the stream, in the run dtype")
+    dim = residual.shape[-1]
+    n_rows = residual.shape[0] if rows is None else rows.numel()
+    if out is not None:
+        _need(out.is_contiguous() and out.shape[0] == n_rows, "rmsnorm_sum: output rows")
+    ptrs = (ctypes.c_void_p * 4)(*[_ptr(d) for d in deltas], *([None] * (4 - len(deltas))))
+    sc = (ctypes.c_float * 4)(*[float(x) for x in scales], *([0.0] * (4 - len(scales))))
+    check(library().pe_rmsnorm_residual_sum(dtype_tag(dt), _ptr(residual), ptrs, sc, len(deltas), _ptr(weight), _ptr(out),
+                                            _ptr(rows), n_rows, dim, float(eps), _stream()), "rmsnorm_residual_sum")
+    _count(1)
+
+
+# ---- recurrences ------------------------------------------------------------------------------------------------------
+def mlstm_recurrence(q, k, v, g, gates: torch.Tensor, gate_bias: torch.Tensor, norm_w: torch.Tensor, cap: float, eps: float,
+                     q_scale: float, out: torch.Tensor, S: torch.Tensor, n: torch.Tensor, m: torch.Tensor,
+                     seq_slot: torch.Tensor, seq_qstart: torch.Tensor, n_seqs: int, heads: int, d: int, dv: int,
+                     status: torch.Tensor) -> None:
+    """csrc/mlstm.cu.  ``q, k, v, g``: views of one row stride in the run dtype; ``gates [N, 2 * heads]`` float32."""
+    ld = q.stride(0)
+    _need(all(t.stride(0) == ld and t.stride(1) == 1 and t.dtype == q.dtype for t in (k, v, g)), "mlstm: q, k, v, g share a row stride")
+    _need(gates.dtype == torch.float32 and gates.is_contiguous() and S.dtype == torch.float32 and S.is_contiguous()
+          and n.is_contiguous() and m.is_contiguous() and out.is_contiguous() and out.dtype == q.dtype, "mlstm: layouts")
+    check(library().pe_mlstm_recurrence(dtype_tag(q.dtype), _ptr(q), _ptr(k), _ptr(v), _ptr(g), ld, _ptr(gates), _ptr(gate_bias),
+                                        _ptr(norm_w), float(cap), float(eps), float(q_scale), _ptr(out), _ptr(S), _ptr(n), _ptr(m),
+                                        _ptr(seq_slot), _ptr(seq_qstart), n_seqs, heads, d, dv, S.shape[0], _ptr(status),
+                                        _stream()), "mlstm_recurrence")
+    _count(1)
+
+
+def short_conv_silu(x: torch.Tensor, col0: int, w: torch.Tensor, tail: torch.Tensor, token_seq: torch.Tensor,
+                    seq_slot: torch.Tensor, seq_qstart: torch.Tensor, out: torch.Tensor, n_seqs: int, status: torch.Tensor) -> None:
+    """Causal convolution over time per channel, then silu; ``tail [slots, taps - 1, channels]`` float32 carries every
+    sequence's last inputs between steps and is brought up to date (csrc/delta_rule.cu)."""
+    channels, taps = w.shape
+    _need(w.dtype == torch.float32 and w.is_contiguous() and tail.dtype == torch.float32 and tail.is_contiguous(), "short_conv: w, tail f32")
+    _need(x.stride(1) == 1 and out.is_contiguous() and out.shape == (x.shape[0], channels) and out.dtype == x.dtype, "short_conv: shapes")
+    _need(taps == 1 or tuple(tail.shape[1:]) == (taps - 1, channels), "short_conv: tail shape")
+    check(library().pe_short_conv_silu(dtype_tag(x.dtype), _ptr(x), x.stride(0), int(col0), _ptr(w), taps, _ptr(tail),
+                                       _ptr(token_seq), _ptr(seq_slot), _ptr(seq_qstart), _ptr(out), x.shape[0], n_seqs, channels,
+                                       tail.shape[0], _ptr(status), _stream()), "short_conv_silu")
+    _count(2 if taps > 1 else 1)
+
+
+def delta_rule_recurrence(qkv: torch.Tensor, a: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, b: torch.Tensor,
+                          gate: torch.Tensor, norm_w: torch.Tensor, eps: float, q_scale: float, out: torch.Tensor,
+                          S: torch.Tensor, seq_slot: torch.Tensor, seq_qstart: torch.Tensor, n_seqs: int, heads: int,
+                          kv_heads: int, d: int, dv: int, status: torch.Tensor) -> None:
+    """csrc/delta_rule.cu.  ``qkv [N, 2 * kv_heads * d + heads * dv]`` after the convolutions; ``a [N, heads * d]`` and
+    ``b [N, heads]`` float32; ``gate [N, heads * dv]`` in the run dtype (any row stride)."""
+    _need(qkv.is_contiguous() and qkv.shape[1] == 2 * kv_heads * d + heads * dv, "delta_rule: q|k|v layout")
+    _need(a.dtype == torch.float32 and a.is_contiguous() and b.dtype == torch.float32 and b.is_contiguous(), "delta_rule: a, b f32")
+    _need(gate.stride(1) == 1 and gate.dtype == qkv.dtype and out.is_contiguous() and S.is_contiguous(), "delta_rule: layouts")
+    check(library().pe_delta_rule_recurrence(dtype_tag(qkv.dtype), _ptr(qkv), _ptr(a), _ptr(dt_bias), _ptr(A_log), _ptr(b),
+                                             _ptr(gate), gate.stride(0), _ptr(norm_w), float(eps), float(q_scale), _ptr(out),
+                                             _ptr(S), _ptr(seq_slot), _ptr(seq_qstart), n_seqs, heads, kv_heads, d, dv,
+                                             S.shape[0], _ptr(status), _stream()), "delta_rule_recurrence")
+    _count(1)
+
+
+# ---- routed experts ---------------------------------------------------------------------------------------------------
+GLU_KINDS = {"silu": 1, "relu": 2, "clamped_swish": 3}
+
+
+def moe_route(logits: torch.Tensor, correction: torch.Tensor, top: int, chosen: torch.Tensor, weight: torch.Tensor) -> None:
+    _need(logits.dtype == torch.float32 and logits.is_contiguous() and correction.dtype == torch.float32, "moe_route: float32 logits")
+    n, n_all = logits.shape
+    _need(chosen.dtype == torch.int32 and weight.dtype == torch.float32 and chosen.numel() == n * top == weight.numel(), "moe_route: outputs")
+    check(library().pe_moe_route(_ptr(logits), _ptr(correction), n, n_all, int(top), _ptr(chosen), _ptr(weight), _stream()), "moe_route")
+    _count(1)
+
+
+def moe_group(chosen: torch.Tensor, n_tokens: int, top: int, n_real: int, offsets: torch.Tensor, row_token: torch.Tensor,
+              pair_row: torch.Tensor) -> None:
+    _need(offsets.numel() == n_real + 1 and row_token.numel() >= n_tokens * top and pair_row.numel() == n_tokens * top, "moe_group: sizes")
+    check(library().pe_moe_group(_ptr(chosen), n_tokens, int(top), int(n_real), _ptr(offsets), _ptr(row_token), _ptr(pair_row),
+                                 _stream()), "moe_group")
+    _count(1)
+
+
+def moe_rows_gemm(x: torch.Tensor, row_map: Optional[torch.Tensor], offsets: torch.Tensor, n_groups: int, max_rows: int,
+                  w: torch.Tensor, out: torch.Tensor, glu: int = 0, limit: float = 0.0, alpha: float = 1.0) -> None:
+    """``out[r] = w[group of r] @ x[row_map[r]]`` for the rows ``offsets[g] .. offsets[g + 1]`` of every group; ``w [groups,
+    n_out (twice with glu), k]``; with ``glu`` the output is act(gate rows, up rows) (csrc/moe.cu)."""
+    _need(w.dim() == 3 and w.is_contiguous() and w.dtype == x.dtype and x.stride(1) == 1 and out.stride(1) == 1, "moe_rows_gemm: layouts")
+    n_out = w.shape[1] // 2 if glu else w.shape[1]
+    _need(out.shape[1] == n_out and x.shape[1] == w.shape[2], "moe_rows_gemm: shapes")
+    check(library().pe_moe_rows_gemm(dtype_tag(x.dtype), dtype_tag(out.dtype), _ptr(x), x.stride(0), _ptr(row_map), _ptr(offsets),
+                                     int(n_groups), int(max_rows), _ptr(w), w.stride(0), _ptr(out), out.stride(0), n_out, w.shape[2],
+                                     int(glu), float(limit), float(alpha), _stream()), "moe_rows_gemm")
+    _count(1)
+
+
+def moe_combine(rows: torch.Tensor, x: torch.Tensor, shared: Optional[torch.Tensor], pair_row: torch.Tensor, weight: torch.Tensor,
+                top: int, out: torch.Tensor) -> None:
+    _need(x.is_contiguous() and out.is_contiguous() and rows.is_contiguous() and rows.shape[1] == x.shape[1], "moe_combine: layouts")
+    _need(shared is None or (shared.is_contiguous() and shared.shape == x.shape), "moe_combine: shared like x")
+    check(library().pe_moe_combine(dtype_tag(x.dtype), _ptr(rows), _ptr(x), _ptr(shared), _ptr(pair_row), _ptr(weight), int(top),
+                                   _ptr(out), x.shape[0], x.shape[1], _stream()), "moe_combine")
+    _count(1)
+
+
+def glu_act(gate_up: torch.Tensor, out: torch.Tensor, kind: str, limit: float = 0.0, alpha: float = 1.0) -> None:
+    """``out = act(gate, up)`` over the halves of ``gate_up [N, 2 * I]``: "silu", "relu", or "clamped_swish"
+    (``g' sigmoid(alpha g') (u' + 1)`` with ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)``)."""
+    _need(gate_up.is_contiguous() and out.is_contiguous() and gate_up.shape[1] == 2 * out.shape[1], "glu_act: shapes")
+    check(library().pe_glu_act(dtype_tag(gate_up.dtype), _ptr(gate_up), _ptr(out), out.shape[0], out.shape[1], GLU_KINDS[kind],
+                               float(limit), float(alpha), _stream()), "glu_act")
+    _count(1)

@@ -7,7 +7,21 @@ from typing import Optional
 
 import torch
 
+from ..kernels import ops
 from .registry import register
+
+
+class DeltaSum:
+    """Several sublayer outputs that are still to be added to the stream, each with a factor: what a block whose
+    sublayers run side by side hands on.  A norm adds them inside its own kernel (``RMSNorm.add_forward``)."""
+
+    def __init__(self, deltas, scales) -> None:
+        self.deltas = list(deltas)
+        self.scales = [float(s) for s in scales]
+
+    def add_into(self, stream: torch.Tensor, weight_like: torch.Tensor) -> None:
+        """``stream += sum_i scale_i * delta_i`` with no norm behind it (``weight_like``: any float32 tensor)."""
+        ops.rmsnorm_residual_sum(stream, self.deltas, self.scales, weight_like, None, 0.0)
 
 
 @register("arrangement", "pre_norm")
@@ -59,7 +73,10 @@ class PostNormBlock:
     def forward(self, stream: torch.Tensor, pending: Optional[torch.Tensor], ctx, view, writes_cache: bool = True):
         rt = self.runtime
         if pending is not None:       # a block before this one left its last delta to be added
-            stream.add_(pending)
+            if isinstance(pending, DeltaSum):
+                pending.add_into(stream, stream)
+            else:
+                stream.add_(pending)
             ctx.stream_copy = None
         same = rt.dtype == torch.float32
         x = stream
@@ -78,3 +95,48 @@ class PostNormBlock:
             x = stream if same else cast
         ctx.stream_copy = None if same else cast
         return None
+
+
+@register("arrangement", "parallel")
+class ParallelBlock:
+    """One norm feeds every sublayer, and their outputs are added together: ``h = norm(x)``;
+    ``x += mult * (sum_i weight_i * mixer_i(h) + ffn(h))``.  Parts by name: ``norm``, any number of mixers (in the
+    order the plan lists them), optionally ``ffn``.  ``BlockSpec.params``: ``mult`` (default 1) and ``mixer_weights``
+    (mixer name -> factor, default 1).  The sum is taken in float32 inside the next norm's kernel, so the block hands
+    its outputs on as a ``DeltaSum``."""
+
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
+    def __init__(self, spec, parts, runtime) -> None:
+        self.runtime = runtime
+        self.name = spec.name
+        self.norm = parts["norm"]
+        self.mixer_names = list(spec.mixer_names())
+        self.mixers = [parts[n] for n in self.mixer_names]
+        self.ffn = parts.get("ffn")
+        mult = float(spec.params.get("mult", 1.0))
+        weights = spec.params.get("mixer_weights") or {}
+        self.scales = [mult * float(weights.get(n, 1.0)) for n in self.mixer_names]
+        self.ffn_scale = mult
+        if len(self.mixers) + (1 if self.ffn is not None else 0) > 4:
+            raise ValueError("a parallel block adds at most four sublayer outputs")
+
+    def forward(self, stream: torch.Tensor, pending, ctx, view, writes_cache: bool = True):
+        rt = self.runtime
+        normed = ctx.buffer("block.normed", tuple(stream.shape), rt.dtype)
+        self.norm.add_forward(stream, pending, normed)
+        deltas = []
+        for i, (name, mixer) in enumerate(zip(self.mixer_names, self.mixers)):
+            v = view[name] if isinstance(view, dict) else view
+            delta = mixer.forward(normed, ctx, v) if writes_cache else mixer.forward(normed, ctx, v, writes_cache=False)
+            if any(type(m) is type(mixer) for m in self.mixers[i + 1:]):
+                # a part's delta lies in a buffer that the next part of its class uses again
+                keep = ctx.buffer(f"block.delta{i}", tuple(delta.shape), delta.dtype)
+                keep.copy_(delta)
+                delta = keep
+            deltas.append(delta)
+        scales = list(self.scales)
+        if self.ffn is not None:
+            deltas.append(self.ffn.forward(normed, ctx))
+            scales.append(self.ffn_scale)
+        return DeltaSum(deltas, scales)

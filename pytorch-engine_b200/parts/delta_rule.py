@@ -1,0 +1,121 @@
+"""The gated delta rule: a linear recurrence whose matrix state forgets per key channel and is corrected by every
+token (the kernels and their formulas: csrc/delta_rule.cu).
+
+For a token with input ``h``, ``kv_heads`` query/key heads of size ``d`` shared by groups of the ``heads`` value heads of
+size ``dv``:
+
+    q, k, v = silu(conv(W_q h)), silu(conv(W_k h)), silu(conv(W_v h))     short causal convolutions per channel
+    q = q / |q| / sqrt(d) ;  k = k / |k|                                   |x| = sqrt(sum x^2 + 1e-6), per head
+    beta = sigmoid(w_b . h) ;  g = exp(-exp(A) softplus(W_a2 W_a1 h + dt)) per head, g also per key channel
+    S <- diag(g) S ;  u = beta (v - S^T k) ;  S <- S + k u^T ;  o = S^T q
+    out = W_o (o / rms_per_head(o) * norm * sigmoid(W_g2 W_g1 h))
+
+What a sequence keeps between steps is of fixed size: every head's ``S [d, dv]`` and the last ``taps - 1`` inputs of the
+convolutions, float32 (a "state" entry of the cache, zero when a slot is taken).  State, decay, beta, the unit vectors
+and the per-head norm are float32 in every run dtype; the decay's and beta's projections write float32.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..kernels import ops
+from .linear import fuse_rows
+from .registry import register
+from .spec import CacheRequest, WeightDecl
+
+
+@register("mixer", "gated_delta")
+class GatedDeltaMixer:
+    """params: ``hidden``, ``n_heads``, ``n_kv_heads``, ``head_dim``, ``v_head_dim``, ``conv`` (taps), ``eps`` (of the
+    per-head norm), ``rank`` (of the decay's and the gate's low-rank projections in a random model; a checkpoint's own
+    tensors decide it).  weights: ``q_proj, k_proj [kv_heads*head_dim, hidden]``, ``v_proj [heads*v_head_dim, hidden]``,
+    ``q_conv, k_conv, v_conv [channels, taps]``, ``b_proj [heads, hidden]``, ``A_log [heads]``, ``a1 [rank, hidden]``, ``a2
+    [heads*head_dim, rank]``, ``dt_bias [heads*head_dim]``, ``g1 [rank, hidden]``, ``g2 [heads*v_head_dim, rank]``, ``norm
+    [v_head_dim]``, ``o_proj [hidden, heads*v_head_dim]``."""
+
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
+    @classmethod
+    def weight_decls(cls, params) -> Dict[str, WeightDecl]:
+        h, nh, nkv, d, dv, taps = (int(params[k]) for k in ("hidden", "n_heads", "n_kv_heads", "head_dim", "v_head_dim", "conv"))
+        rank = int(params.get("rank", 16))
+        return {"q_proj": WeightDecl((nkv * d, h)), "k_proj": WeightDecl((nkv * d, h)), "v_proj": WeightDecl((nh * dv, h)),
+                "q_conv": WeightDecl((nkv * d, taps)), "k_conv": WeightDecl((nkv * d, taps)), "v_conv": WeightDecl((nh * dv, taps)),
+                "b_proj": WeightDecl((nh, h)), "A_log": WeightDecl((nh,)),
+                "a1": WeightDecl((rank, h), any_dims=(0,)), "a2": WeightDecl((nh * d, rank), any_dims=(1,)),
+                "dt_bias": WeightDecl((nh * d,)),
+                "g1": WeightDecl((rank, h), any_dims=(0,)), "g2": WeightDecl((nh * dv, rank), any_dims=(1,)),
+                "norm": WeightDecl((dv,), "norm"), "o_proj": WeightDecl((h, nh * dv))}
+
+    @classmethod
+    def cache_request(cls, params) -> Optional[CacheRequest]:
+        nh, nkv, d, dv, taps = (int(params[k]) for k in ("n_heads", "n_kv_heads", "head_dim", "v_head_dim", "conv"))
+        shapes = [("S", (nh, d, dv), "float32")]
+        if taps > 1:
+            shapes.append(("conv", (taps - 1, 2 * nkv * d + nh * dv), "float32"))
+        return CacheRequest(kind="state", state_shapes=tuple(shapes))
+
+    def __init__(self, params, weights, runtime) -> None:
+        self.runtime = runtime
+        self.hidden = int(params["hidden"])
+        self.n_heads = int(params["n_heads"])
+        self.n_kv_heads = int(params["n_kv_heads"])
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError("n_heads must be a multiple of n_kv_heads")
+        self.head_dim = int(params["head_dim"])
+        self.v_dim = int(params["v_head_dim"])
+        self.taps = int(params["conv"])
+        self.eps = float(params.get("eps", 1e-5))
+        if self.v_dim > 1024 or (self.head_dim * self.v_dim + 3 * self.head_dim) * 4 > 200 * 1024:
+            raise ValueError(f"a head of {self.head_dim} x {self.v_dim} is beyond what the recurrence kernel keeps in shared memory")
+        f32 = torch.float32
+        self.rank_a, self.rank_g = int(weights["a1"].shape[0]), int(weights["g1"].shape[0])
+        if weights["a2"].shape[1] != self.rank_a or weights["g2"].shape[1] != self.rank_g:
+            raise ValueError("the two halves of a low-rank projection do not fit")
+        self.channels = 2 * self.n_kv_heads * self.head_dim + self.n_heads * self.v_dim
+        # q | k | v | the low ranks of decay and gate: one product over the mixer's input
+        self.wide = fuse_rows(runtime, [weights["q_proj"], weights["k_proj"], weights["v_proj"], weights["a1"], weights["g1"]])
+        self.conv_w = torch.cat([weights[f"{s}_conv"].to(device=runtime.device, dtype=f32) for s in "qkv"]).contiguous()
+        self.b_proj = runtime.adopt(weights["b_proj"])
+        self.a2 = runtime.adopt(weights["a2"])
+        self.g2 = runtime.adopt(weights["g2"])
+        self.A_log = runtime.adopt(weights["A_log"], f32)
+        self.dt_bias = runtime.adopt(weights["dt_bias"], f32)
+        self.norm = runtime.adopt(weights["norm"], f32)
+        self.o_proj = runtime.adopt(weights["o_proj"])
+        self.no_tail = torch.zeros((1,), dtype=f32, device=runtime.device)
+
+    def _f32_linear(self, x, w, buf):
+        y = self.runtime.linear(x, w, out=buf, out_dtype=torch.float32)
+        if y.data_ptr() != buf.data_ptr():
+            buf.copy_(y)
+        return buf
+
+    def forward(self, x: torch.Tensor, ctx, view, writes_cache: bool = True) -> torch.Tensor:
+        if not writes_cache:
+            raise ValueError("a gated delta mixer folds every token into its state; it cannot run without writing it")
+        rt = self.runtime
+        n = x.shape[0]
+        c, ra = self.channels, self.rank_a
+        wide = ctx.buffer("delta.wide", (n, c + ra + self.rank_g), rt.dtype)
+        rt.linear(x, self.wide, out=wide)
+        qkv = ctx.buffer("delta.qkv", (n, c), rt.dtype)
+        tail = view.state("conv") if self.taps > 1 else self.no_tail
+        ops.short_conv_silu(wide, 0, self.conv_w, tail, ctx.token_seq, ctx.seq_slot, ctx.seq_qstart, qkv, ctx.n_seqs, rt.status)
+        low_a = ctx.buffer("delta.low_a", (n, ra), rt.dtype)
+        low_a.copy_(wide[:, c:c + ra])
+        low_g = ctx.buffer("delta.low_g", (n, self.rank_g), rt.dtype)
+        low_g.copy_(wide[:, c + ra:])
+        decay = self._f32_linear(low_a, self.a2, ctx.buffer("delta.decay", (n, self.n_heads * self.head_dim), torch.float32))
+        beta = self._f32_linear(x, self.b_proj, ctx.buffer("delta.beta", (n, self.n_heads), torch.float32))
+        gate = ctx.buffer("delta.gate", (n, self.n_heads * self.v_dim), rt.dtype)
+        rt.linear(low_g, self.g2, out=gate)
+        out = ctx.buffer("delta.out", (n, self.n_heads * self.v_dim), rt.dtype)
+        ops.delta_rule_recurrence(qkv, decay, self.dt_bias, self.A_log, beta, gate, self.norm, self.eps, self.head_dim ** -0.5,
+                                  out, view.state("S"), ctx.seq_slot, ctx.seq_qstart, ctx.n_seqs, self.n_heads,
+                                  self.n_kv_heads, self.head_dim, self.v_dim, rt.status)
+        delta = ctx.buffer("delta.delta", (n, self.hidden), rt.dtype)
+        rt.linear(out, self.o_proj, out=delta)
+        return delta

@@ -7,7 +7,7 @@ import torch
 
 from ..kernels import ops
 from .registry import register
-from .spec import WeightDecl
+from .spec import CacheRequest, WeightDecl
 
 
 @register("embedding", "token_embedding")
@@ -29,6 +29,43 @@ class TokenEmbedding:
 
     def forward(self, token_ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         ops.embed_gather(self.weight, token_ids, out, self.runtime.status)
+        return out
+
+
+@register("embedding", "token_pair_embedding")
+class TokenPairEmbedding:
+    """A token embedding plus an embedding of the pair (previous token, token), hashed into a table:
+    ``x = E[tok] + B[(prev * mul_prev + tok * mul_cur) mod buckets]``, and ``B[buckets]`` (the table's last row) for a
+    sequence's first token.  params: ``vocab``, ``hidden``, ``buckets``, ``mul_prev``, ``mul_cur``.  weights: ``weight
+    [vocab, hidden]``, ``pairs [buckets + 1, hidden]``.  What a sequence keeps between steps is its last token (a
+    "state" entry of the cache: one int32)."""
+
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
+    @classmethod
+    def weight_decls(cls, params) -> Dict[str, WeightDecl]:
+        h = int(params["hidden"])
+        return {"weight": WeightDecl((int(params["vocab"]), h), "embedding"),
+                "pairs": WeightDecl((int(params["buckets"]) + 1, h), "embedding")}
+
+    @classmethod
+    def cache_request(cls, params) -> CacheRequest:
+        return CacheRequest(kind="state", state_shapes=(("last_token", (1,), "int32"),))
+
+    def __init__(self, params, weights, runtime) -> None:
+        self.runtime = runtime
+        self.vocab = int(params["vocab"])
+        self.hidden = int(params["hidden"])
+        self.buckets = int(params["buckets"])
+        self.mul_prev = int(params["mul_prev"])
+        self.mul_cur = int(params["mul_cur"])
+        self.weight = runtime.adopt(weights["weight"])
+        self.pairs = runtime.adopt(weights["pairs"])
+
+    def forward(self, token_ids: torch.Tensor, out: torch.Tensor, ctx, view) -> torch.Tensor:
+        last = view.state("last_token").view(-1)
+        ops.embed_pair_gather(self.weight, self.pairs, token_ids, ctx.token_seq, ctx.token_pos, ctx.seq_slot, ctx.seq_qstart,
+                              last, out, self.buckets, self.mul_prev, self.mul_cur, self.runtime.status)
         return out
 
 

@@ -1,0 +1,96 @@
+"""Routed experts: a router picks a few small gated feed-forwards per token, optionally among them "identity experts"
+that return their input, optionally with a shared expert that every token passes (the kernels: csrc/moe.cu).
+
+    z = R h (float32) ;  s = softmax(z) over all router outputs
+    chosen = the ``top`` largest of s + correction ;  their weights are s itself, not renormalised
+    y = sum_chosen s_e * expert_e(h)  (+ shared(h)) ;  expert_e(h) = h for e >= n_experts (identity experts)
+    expert(h) = D act(G h, U h)  with the activations of ``parts/swiglu.py``
+
+The (token, choice) pairs are grouped by expert on the device and every expert's rows go through its matrices in one
+launch per product, so nothing is read back to the host and a decode step stays recordable.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..kernels import ops
+from .registry import register
+from .spec import WeightDecl
+from .swiglu import SwiGLU
+
+
+@register("feed_forward", "routed_experts")
+class RoutedExperts:
+    """params: ``hidden``, ``n_experts``, ``n_identity`` (router outputs beyond the real experts), ``top``, ``intermediate``,
+    ``activation`` / ``limit`` / ``alpha`` (of every expert), ``shared`` (None, or the params of a ``swiglu`` part).
+    weights: ``router [n_experts + n_identity, hidden]``, ``correction [n_experts + n_identity]``, ``e<i>.gate, e<i>.up
+    [I, H]``, ``e<i>.down [H, I]``, and ``shared.gate, shared.up, shared.down`` with a shared expert."""
+
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
+    @classmethod
+    def weight_decls(cls, params) -> Dict[str, WeightDecl]:
+        h, n, extra, inter = (int(params[k]) for k in ("hidden", "n_experts", "n_identity", "intermediate"))
+        decls = {"router": WeightDecl((n + extra, h)), "correction": WeightDecl((n + extra,))}
+        for e in range(n):
+            decls[f"e{e}.gate"] = WeightDecl((inter, h))
+            decls[f"e{e}.up"] = WeightDecl((inter, h))
+            decls[f"e{e}.down"] = WeightDecl((h, inter))
+        if params.get("shared"):
+            si = int(params["shared"]["intermediate"])
+            decls.update({"shared.gate": WeightDecl((si, h)), "shared.up": WeightDecl((si, h)), "shared.down": WeightDecl((h, si))})
+        return decls
+
+    def __init__(self, params, weights, runtime) -> None:
+        self.runtime = runtime
+        self.hidden = int(params["hidden"])
+        self.n_experts = int(params["n_experts"])
+        self.n_identity = int(params["n_identity"])
+        self.top = int(params["top"])
+        self.intermediate = int(params["intermediate"])
+        if not 1 <= self.top <= self.n_experts + self.n_identity:
+            raise ValueError(f"top = {self.top} experts of {self.n_experts + self.n_identity}")
+        self.activation = str(params.get("activation") or "silu")
+        self.glu = ops.GLU_KINDS[self.activation]
+        self.limit = float(params.get("limit") or 0.0)
+        self.alpha = float(params.get("alpha") or 1.0)
+        dev, dt = runtime.device, runtime.dtype
+        self.router = runtime.adopt(weights["router"])
+        self.correction = runtime.adopt(weights["correction"], torch.float32)
+        if self.n_experts:
+            self.gate_up = torch.stack([torch.cat([weights[f"e{e}.gate"], weights[f"e{e}.up"]]).to(device=dev, dtype=dt)
+                                        for e in range(self.n_experts)]).contiguous()
+            self.down = torch.stack([weights[f"e{e}.down"].to(device=dev, dtype=dt) for e in range(self.n_experts)]).contiguous()
+        self.shared = None
+        if params.get("shared"):
+            sp = dict(params["shared"])
+            sp["hidden"] = self.hidden
+            self.shared = SwiGLU(sp, {"gate_proj": weights["shared.gate"], "up_proj": weights["shared.up"],
+                                      "down_proj": weights["shared.down"]}, runtime)
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        rt = self.runtime
+        n, top = x.shape[0], self.top
+        n_all = self.n_experts + self.n_identity
+        logits = ctx.buffer("moe.logits", (n, n_all), torch.float32)
+        y = rt.linear(x, self.router, out=logits, out_dtype=torch.float32)
+        if y.data_ptr() != logits.data_ptr():
+            logits.copy_(y)
+        chosen = ctx.buffer("moe.chosen", (n, top), torch.int32)
+        weight = ctx.buffer("moe.weight", (n, top), torch.float32)
+        ops.moe_route(logits, self.correction, top, chosen, weight)
+        offsets = ctx.buffer("moe.offsets", (self.n_experts + 1,), torch.int32)
+        row_token = ctx.buffer("moe.row_token", (n * top,), torch.int32)
+        pair_row = ctx.buffer("moe.pair_row", (n, top), torch.int32)
+        ops.moe_group(chosen, n, top, self.n_experts, offsets, row_token, pair_row)
+        rows = ctx.buffer("moe.rows", (n * top, self.hidden), rt.dtype)
+        if self.n_experts:
+            act = ctx.buffer("moe.act", (n * top, self.intermediate), rt.dtype)
+            ops.moe_rows_gemm(x, row_token, offsets, self.n_experts, n * top, self.gate_up, act, self.glu, self.limit, self.alpha)
+            ops.moe_rows_gemm(act, None, offsets, self.n_experts, n * top, self.down, rows)
+        shared = self.shared.forward(x, ctx) if self.shared is not None else None
+        delta = ctx.buffer("moe.delta", (n, self.hidden), rt.dtype)
+        ops.moe_combine(rows, x, shared, pair_row, weight, top, delta)
+        return delta

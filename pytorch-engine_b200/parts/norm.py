@@ -29,6 +29,9 @@ class RMSNorm:
 
     def add_forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
                     rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if hasattr(delta, "deltas"):      # several scaled outputs of a block whose sublayers run side by side
+            ops.rmsnorm_residual_sum(residual, delta.deltas, delta.scales, self.weight, out, self.eps, rows)
+            return out
         ops.rmsnorm_residual(residual, delta, self.weight, out, self.eps, rows)
         return out
 

@@ -27,7 +27,8 @@ from .spec import WeightDecl
 @register("position", "rope")
 class RotaryPosition:
     """params: ``rotary_dim`` (even, <= head size), ``theta``, ``max_positions``, ``style`` ("neox" or
-    "interleaved"), ``scaling`` (None, or a mapping with factor, original, fast, slow).  The tables hold
+    "interleaved"), ``scaling`` (None, or a mapping with factor, original, fast, slow), ``exact`` (true: the tables are
+    computed in float64 and rounded once; otherwise the angle is a float32 product, as the reference has it).  The tables hold
     ``max_positions`` rows, or as many as the engine can hold in one sequence if that is fewer
     (``runtime.position_limit``)."""
 
@@ -54,6 +55,13 @@ class RotaryPosition:
             raise ValueError(f"rotary_dim must be positive and even, got {self.rotary_dim}")
         scaling = params.get("scaling")
         mult = 1.0
+        if params.get("exact") and not scaling:
+            # frequencies, angles, cos and sin in float64 on the host, each table entry rounded once to float32
+            idx = torch.arange(0, self.rotary_dim, 2, dtype=torch.float64)
+            ang = torch.outer(torch.arange(0, self.max_positions, dtype=torch.float64), self.theta ** (-idx / self.rotary_dim))
+            self.cos = torch.cos(ang).to(torch.float32).to(runtime.device).contiguous()
+            self.sin = torch.sin(ang).to(torch.float32).to(runtime.device).contiguous()
+            return
         if not scaling:
             idx = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32)
             inv_freq = (1.0 / (self.theta ** (idx / self.rotary_dim))).to(runtime.device)

@@ -38,6 +38,8 @@ class BlockSpec:
     arrangement: str
     parts: Mapping[str, Tuple[str, PartSpec]]
     name: str = ""
+    # constants of the arrangement itself (a factor on what the block adds, a weight per mixer)
+    params: Mapping[str, Any] = field(default_factory=dict)
 
     @classmethod
     def standard(cls, arrangement: str, mixer_norm: PartSpec, mixer: PartSpec, ffn_norm: PartSpec, ffn: PartSpec,

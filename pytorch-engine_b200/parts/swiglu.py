@@ -14,7 +14,12 @@ from .spec import WeightDecl
 
 @register("feed_forward", "swiglu")
 class SwiGLU:
-    """params: ``hidden``, ``intermediate``.  weights: ``gate_proj, up_proj [I, H]``, ``down_proj [H, I]``."""
+    """params: ``hidden``, ``intermediate``.  weights: ``gate_proj, up_proj [I, H]``, ``down_proj [H, I]``.
+
+    Optional params: ``activation`` ("silu", the default; "relu": ``relu(gate) * up``; "clamped_swish": ``g' sigmoid(alpha
+    g') (u' + 1)`` with ``g' = min(gate, limit)``, ``u' = clamp(up, -limit, limit)``), with ``limit`` and ``alpha``.  The
+    fused epilogues of the product kernels are SiLU's; another activation runs as a kernel of its own behind the
+    gate|up product."""
 
     graph_safe = True  # launches only; nothing in forward() waits for the device
 
@@ -27,6 +32,11 @@ class SwiGLU:
         self.runtime = runtime
         self.hidden = int(params["hidden"])
         self.intermediate = int(params["intermediate"])
+        self.activation = str(params.get("activation") or "silu")
+        if self.activation not in ops.GLU_KINDS:
+            raise ValueError(f"activation {self.activation!r} is not built ({', '.join(sorted(ops.GLU_KINDS))} are)")
+        self.limit = float(params.get("limit") or 0.0)
+        self.alpha = float(params.get("alpha") or 1.0)
         self.gate_up = fuse_rows(runtime, [weights["gate_proj"], weights["up_proj"]])
         self.down = runtime.adopt(weights["down_proj"])
 
@@ -34,7 +44,11 @@ class SwiGLU:
         rt = self.runtime
         n = x.shape[0]
         act = ctx.buffer("ffn.act", (n, self.intermediate), rt.dtype)
-        if rt.takes_small_gemm(x, self.gate_up):
+        if self.activation != "silu":
+            gu = ctx.buffer("ffn.gate_up", (n, 2 * self.intermediate), rt.dtype)
+            rt.linear(x, self.gate_up, out=gu)
+            ops.glu_act(gu, act, self.activation, self.limit, self.alpha)
+        elif rt.takes_small_gemm(x, self.gate_up):
             # few rows: gate|up product with silu(gate) * up in its epilogue
             ops.gemm_smallm(x, self.gate_up, act, pair_offset=self.intermediate)
         elif rt.takes_large_gemm(x, self.gate_up, self.intermediate):
