@@ -141,8 +141,9 @@ int pe_rmsnorm_residual_sum(int dtype, float* residual, const void* const* delta
 // mlstm.cu
 int pe_mlstm_recurrence(int dtype, const void* q, const void* k, const void* v, const void* g, long long ld,
     const float* gates, const float* gate_bias, const float* norm_w, float cap, float eps, float q_scale, void* out,
-    float* S, float* n, float* m, const int* seq_slot, const int* seq_qstart, int n_seqs, int heads, int d, int dv,
-    int n_slots, int* status, cudaStream_t stream);
+    float* S, float* n, float* m, const int* seq_slot, const int* seq_qstart, int n_seqs, int max_q, int heads, int d,
+    int dv, int n_slots, int chunk, int max_chunks, float* scratch, int* status, cudaStream_t stream);
+long long pe_mlstm_scratch_floats(int n_seqs, int heads, int d, int dv, int max_chunks);
 
 // delta_rule.cu
 int pe_short_conv_silu(int dtype, const void* x, long long ld, int col0, const float* w, int taps, float* tail,
@@ -150,8 +151,9 @@ int pe_short_conv_silu(int dtype, const void* x, long long ld, int col0, const f
     int n_slots, int* status, cudaStream_t stream);
 int pe_delta_rule_recurrence(int dtype, const void* qkv, const float* a, const float* dt_bias, const float* A_log,
     const float* b, const void* gate, long long gate_ld, const float* norm_w, float eps, float q_scale, void* out, float* S,
-    const int* seq_slot, const int* seq_qstart, int n_seqs, int heads, int kv_heads, int d, int dv, int n_slots,
-    int* status, cudaStream_t stream);
+    const int* seq_slot, const int* seq_qstart, int n_seqs, int max_q, int heads, int kv_heads, int d, int dv, int n_slots,
+    int chunk, int max_chunks, float* scratch, int* status, cudaStream_t stream);
+long long pe_delta_rule_scratch_floats(int n_seqs, int heads, int d, int dv, int max_chunks);
 
 // moe.cu
 int pe_moe_route(const float* logits, const float* correction, int n_tokens, int n_all, int top, int* chosen,

@@ -82,69 +82,146 @@ struct DeltaArgs {
   float* S;                 // [slots, heads, d, dv]
   const int* seq_slot; const int* seq_qstart;
   int n_seqs, heads, kv_heads, d, dv, n_slots;
+  int chunk;                // tokens per chunk (modes 1 and 3), 0: the whole step in one go
+  int max_chunks;
+  float* scratch;           // [n_seqs, max_chunks, heads, d * dv + d * d]: a chunk's S, then its transition matrix
   int* status;
 };
 
-template <typename T>
-__global__ void delta_rule_kernel(DeltaArgs a) {
+__host__ __device__ inline size_t delta_unit(int d, int dv) { return (size_t)d * dv + (size_t)d * d; }
+
+// MODE 0: the whole step: start from the slot's state, write outputs, write the state back.
+// MODE 1: chunk c = blockIdx.z % max_chunks from an empty state, no outputs.  A token's step is linear in S,
+//         S <- (I - beta k k^T) diag(g) S + beta k v^T, and every column of S goes its own way; so the chunk's end
+//         state from zero (blockIdx.z < max_chunks: the columns of S) and the product of its tokens' transition
+//         matrices (blockIdx.z >= max_chunks: the same step on the columns of a d x d matrix that starts as the
+//         identity and is fed v = 0) are both left for the chain kernel: S_start[c+1] = T_c S_start[c] + S_chunk[c].
+// MODE 3: chunk blockIdx.z from its true start (as the chain kernel left it): writes outputs; the sequence's last chunk
+//         writes the state back.
+// DREG > 0: d <= DREG and thread j keeps its column in registers; DREG == 0: the matrix lives in shared memory.
+template <typename T, int MODE, int DREG>
+__global__ void __launch_bounds__(DREG == 0 ? 1024 : (DREG == 32 ? 512 : 256)) delta_rule_kernel(DeltaArgs a) {
   extern __shared__ float sm[];
   __shared__ float red[32];
-  const int d = a.d, dv = a.dv, head = blockIdx.x, b = blockIdx.y;
+  const int d = a.d, head = blockIdx.x, b = blockIdx.y;
+  const int c = MODE == 1 ? blockIdx.z % a.max_chunks : blockIdx.z;
+  const bool transition = MODE == 1 && (int)blockIdx.z >= a.max_chunks;
+  const int dv = a.dv;
+  const int cols = transition ? d : dv;            // columns of the matrix this block carries
   const int kvh = head / (a.heads / a.kv_heads);
-  float* S = sm;               // [d][dv]
-  float* qs = S + (size_t)d * dv;
-  float* ks = qs + d;
-  float* gs = ks + d;
+  constexpr int DP = DREG > 0 ? DREG : 1;
+  const int dpad = DREG > 0 ? DREG : d;
+  float* S = sm;                                   // [d][cols] (DREG == 0 only)
+  float* qs = S + (DREG > 0 ? 0 : (size_t)d * (dv > d ? dv : d));
+  float* ks = qs + dpad;
+  float* gs = ks + dpad;
   pdl_wait_block();
   pdl_launch_dependents();
   const int slot = a.seq_slot[b];
   if (slot < 0 || slot >= a.n_slots) {
-    if (threadIdx.x == 0 && head == 0) report(a.status, kStatusSlotOutOfRange, b, slot, a.n_slots);
+    if (threadIdx.x == 0 && head == 0 && blockIdx.z == 0) report(a.status, kStatusSlotOutOfRange, b, slot, a.n_slots);
     return;
   }
-  const int t0 = a.seq_qstart[b], t1 = a.seq_qstart[b + 1];
+  const int q0 = a.seq_qstart[b], q1 = a.seq_qstart[b + 1];
+  int t0 = q0, t1 = q1;
+  if (MODE != 0) {
+    t0 = q0 + c * a.chunk;
+    t1 = min(q1, t0 + a.chunk);
+    if (t0 >= q1) return;
+    if (MODE == 1 && t1 == q1) return;             // nothing follows the sequence's last chunk
+  }
+  const size_t unit = delta_unit(d, dv);
+  float* cs = MODE != 0 ? a.scratch + (((size_t)b * a.max_chunks + c) * a.heads + head) * unit : nullptr;
   float* gS = a.S + ((size_t)slot * a.heads + head) * d * dv;
-  for (int i = threadIdx.x; i < d * dv; i += blockDim.x) S[i] = gS[i];
+  const float* src = MODE == 0 ? gS : cs;
   const int j = threadIdx.x;
+  float Sr[DP];
+  if (MODE == 1) {
+    if (DREG > 0) {
+#pragma unroll
+      for (int i = 0; i < DP; ++i) Sr[i] = (transition && i == j) ? 1.f : 0.f;
+    } else {
+      for (int i = threadIdx.x; i < d * cols; i += blockDim.x) S[i] = (transition && i / cols == i % cols) ? 1.f : 0.f;
+    }
+  } else {
+    if (DREG > 0) {
+#pragma unroll
+      for (int i = 0; i < DP; ++i) Sr[i] = (i < d && j < dv) ? src[(size_t)i * dv + j] : 0.f;
+    } else {
+      for (int i = threadIdx.x; i < d * dv; i += blockDim.x) S[i] = src[i];
+    }
+  }
+  for (int i = d + threadIdx.x; i < dpad; i += blockDim.x) { qs[i] = 0.f; ks[i] = 0.f; gs[i] = 0.f; }
   const int channels = 2 * a.kv_heads * d + a.heads * dv;
   const int k_col = a.kv_heads * d, v_col = 2 * a.kv_heads * d;
   const T* x = (const T*)a.qkv;
   const float rate = expf(a.A_log[head]);
-  const float nw = j < dv ? a.norm_w[j] : 0.f;
+  const float nw = (MODE != 1 && j < dv) ? a.norm_w[j] : 0.f;
   __syncthreads();
   for (int t = t0; t < t1; ++t) {
     float q2 = 0.f, k2 = 0.f;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
-      const float qq = to_f32<T>(x[(size_t)t * channels + kvh * d + i]);
       const float kk = to_f32<T>(x[(size_t)t * channels + k_col + kvh * d + i]);
-      qs[i] = qq;
       ks[i] = kk;
-      q2 += qq * qq;
       k2 += kk * kk;
+      if (MODE != 1) {
+        const float qq = to_f32<T>(x[(size_t)t * channels + kvh * d + i]);
+        qs[i] = qq;
+        q2 += qq * qq;
+      }
       const float z = a.a[(size_t)t * a.heads * d + head * d + i] + a.dt_bias[head * d + i];
       const float softplus = z > 20.f ? z : log1pf(expf(z));
       gs[i] = expf(-rate * softplus);
     }
-    q2 = block_sum(q2, red);
     k2 = block_sum(k2, red);
+    if (MODE != 1) q2 = block_sum(q2, red);
     const float qn = rsqrtf(q2 + 1e-6f) * a.q_scale, kn = rsqrtf(k2 + 1e-6f);
     const float beta = 1.f / (1.f + expf(-a.b[(size_t)t * a.heads + head]));
     float o = 0.f;
-    if (j < dv) {
+    if (j < cols) {
       float acc = 0.f;
-      for (int i = 0; i < d; ++i) {
-        const float s = gs[i] * S[(size_t)i * dv + j];
-        S[(size_t)i * dv + j] = s;
-        acc = fmaf(s, ks[i], acc);
-      }
-      const float u = beta * (to_f32<T>(x[(size_t)t * channels + v_col + head * dv + j]) - acc * kn);
-      const float uk = u * kn;
-      for (int i = 0; i < d; ++i) {
-        const float s = fmaf(ks[i], uk, S[(size_t)i * dv + j]);
-        S[(size_t)i * dv + j] = s;
-        o = fmaf(s, qs[i], o);
+      const float vj = transition ? 0.f : to_f32<T>(x[(size_t)t * channels + v_col + head * dv + j]);
+      if (DREG > 0) {
+#pragma unroll
+        for (int i = 0; i < DP; i += 4) {
+          const float4 g4 = *reinterpret_cast<const float4*>(gs + i);
+          const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            Sr[i + e] *= (&g4.x)[e];
+            acc = fmaf(Sr[i + e], (&k4.x)[e], acc);
+          }
+        }
+        const float uk = beta * (vj - acc * kn) * kn;
+#pragma unroll
+        for (int i = 0; i < DP; i += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) Sr[i + e] = fmaf((&k4.x)[e], uk, Sr[i + e]);
+          if (MODE != 1) {
+            const float4 q4 = *reinterpret_cast<const float4*>(qs + i);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o = fmaf(Sr[i + e], (&q4.x)[e], o);
+          }
+        }
+      } else {
+        for (int i = 0; i < d; ++i) {
+          const float s = gs[i] * S[(size_t)i * cols + j];
+          S[(size_t)i * cols + j] = s;
+          acc = fmaf(s, ks[i], acc);
+        }
+        const float uk = beta * (vj - acc * kn) * kn;
+        for (int i = 0; i < d; ++i) {
+          const float s = fmaf(ks[i], uk, S[(size_t)i * cols + j]);
+          S[(size_t)i * cols + j] = s;
+          if (MODE != 1) o = fmaf(s, qs[i], o);
+        }
       }
       o *= qn;
+    }
+    if (MODE == 1) {
+      __syncthreads();                             // this token's k and g have been read before the next are written
+      continue;
     }
     const float ss = block_sum(o * o, red);
     if (j < dv) {
@@ -154,7 +231,99 @@ __global__ void delta_rule_kernel(DeltaArgs a) {
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < d * dv; i += blockDim.x) gS[i] = S[i];
+  if (MODE == 3 && t1 != q1) return;               // only the sequence's last chunk leaves the state
+  float* dst = MODE == 1 ? (transition ? cs + (size_t)d * dv : cs) : gS;
+  if (DREG > 0) {
+    if (j < cols) {
+#pragma unroll
+      for (int i = 0; i < DP; ++i)
+        if (i < d) dst[(size_t)i * cols + j] = Sr[i];
+    }
+  } else {
+    for (int i = threadIdx.x; i < d * cols; i += blockDim.x) dst[i] = S[i];
+  }
+}
+
+// Chain the chunks: on entry scratch[c] holds chunk c's end state from zero and its transition matrix (every chunk
+// but the sequence's last); on exit its S part holds chunk c's true start state, chunk 0's being the slot's state.
+// A block takes a few columns of one head's state: thread (i, col) keeps element i of its column, the chunk's
+// transition matrix passes through shared memory (rows padded by one float, so that a read across i has no conflicts).
+__global__ void delta_chain_kernel(DeltaArgs a, int col_tile) {
+  extern __shared__ float sm[];
+  const int d = a.d, dv = a.dv, head = blockIdx.x, b = blockIdx.y;
+  float* Ts = sm;                                  // [d][d + 1]
+  float* cur = Ts + (size_t)d * (d + 1);           // [col_tile][d]
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int slot = a.seq_slot[b];
+  if (slot < 0 || slot >= a.n_slots) return;
+  const int q_len = a.seq_qstart[b + 1] - a.seq_qstart[b];
+  const int n_chunks = (q_len + a.chunk - 1) / a.chunk;
+  const int i = threadIdx.x % d, cj = threadIdx.x / d;
+  const int j = blockIdx.z * col_tile + cj;
+  const bool live = cj < col_tile && j < dv;
+  const size_t unit = delta_unit(d, dv);
+  float* cs = a.scratch + ((size_t)b * a.max_chunks * a.heads + head) * unit;
+  const size_t per = (size_t)a.heads * unit;
+  float val = live ? a.S[((size_t)slot * a.heads + head) * d * dv + (size_t)i * dv + j] : 0.f;
+  for (int c = 0; c < n_chunks; ++c) {
+    float* u = cs + (size_t)c * per;
+    const bool has = c + 1 < n_chunks;
+    const float loc = (has && live) ? u[(size_t)i * dv + j] : 0.f;
+    if (live) u[(size_t)i * dv + j] = val;
+    if (!has) break;
+    const float* Tg = u + (size_t)d * dv;
+    for (int e = threadIdx.x; e < d * d; e += blockDim.x) Ts[(size_t)(e / d) * (d + 1) + e % d] = Tg[e];
+    if (cj < col_tile) cur[(size_t)cj * d + i] = val;
+    __syncthreads();
+    float acc = loc;
+    if (live) {
+      const float* trow = Ts + (size_t)i * (d + 1);
+      const float* col = cur + (size_t)cj * d;
+      for (int k = 0; k < d; ++k) acc = fmaf(trow[k], col[k], acc);
+    }
+    val = acc;
+    __syncthreads();
+  }
+}
+
+template <typename T, int DREG>
+static int delta_run(const DeltaArgs& a, cudaStream_t stream) {
+  const int d = a.d, dv = a.dv;
+  const int dpad = DREG > 0 ? DREG : d;
+  const int widest = dv > d ? dv : d;
+  const size_t smem = ((DREG > 0 ? 0 : (size_t)d * widest) + 3 * (size_t)dpad) * sizeof(float);
+  int threads = (widest + 31) / 32 * 32;
+  const int cap_threads = DREG == 0 ? 1024 : (DREG == 32 ? 512 : 256);
+  if (threads > cap_threads) threads = cap_threads;
+  if (widest > threads) return PE_ERR_UNSUPPORTED_SIZE;
+  auto k0 = delta_rule_kernel<T, 0, DREG>;
+  auto k1 = delta_rule_kernel<T, 1, DREG>;
+  auto k3 = delta_rule_kernel<T, 3, DREG>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  if (a.chunk > 0) {
+    launch(k1, dim3(a.heads, a.n_seqs, 2 * a.max_chunks), dim3(threads), smem, stream, a);
+    int col_tile = 1024 / d;
+    if (col_tile > 8) col_tile = 8;
+    if (col_tile < 1) return PE_ERR_UNSUPPORTED_SIZE;
+    const size_t chain_smem = ((size_t)d * (d + 1) + (size_t)col_tile * d) * sizeof(float);
+    if (chain_smem > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;
+    if (chain_smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(delta_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)chain_smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    launch(delta_chain_kernel, dim3(a.heads, a.n_seqs, (dv + col_tile - 1) / col_tile), dim3(col_tile * d), chain_smem, stream, a,
+           col_tile);
+    launch(k3, dim3(a.heads, a.n_seqs, a.max_chunks), dim3(threads), smem, stream, a);
+  } else {
+    launch(k0, dim3(a.heads, a.n_seqs, 1), dim3(threads), smem, stream, a);
+  }
+  return PE_OK;
 }
 
 }  // namespace pe
@@ -186,26 +355,39 @@ extern "C" int pe_short_conv_silu(int dtype, const void* x, long long ld, int co
   return PE_OK;
 }
 
+// Floats of scratch that the chunked form needs for `max_chunks` chunks per sequence.
+extern "C" long long pe_delta_rule_scratch_floats(int n_seqs, int heads, int d, int dv, int max_chunks) {
+  return (long long)n_seqs * max_chunks * heads * (long long)pe::delta_unit(d, dv);
+}
+
+// chunk > 0: prompts cut into chunks of that many tokens (scratch from pe_delta_rule_scratch_floats, max_chunks >=
+// ceil(max_q / chunk)); chunk == 0: each sequence's tokens in one go (single tokens, short prompts).
 extern "C" int pe_delta_rule_recurrence(int dtype, const void* qkv, const float* a, const float* dt_bias, const float* A_log,
                                         const float* b, const void* gate, long long gate_ld, const float* norm_w, float eps,
                                         float q_scale, void* out, float* S, const int* seq_slot, const int* seq_qstart,
-                                        int n_seqs, int heads, int kv_heads, int d, int dv, int n_slots, int* status,
-                                        cudaStream_t stream) {
+                                        int n_seqs, int max_q, int heads, int kv_heads, int d, int dv, int n_slots, int chunk,
+                                        int max_chunks, float* scratch, int* status, cudaStream_t stream) {
   if (n_seqs <= 0) return PE_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || d <= 0 || dv <= 0) return PE_ERR_BAD_ARGUMENT;
-  const size_t smem = ((size_t)d * dv + 3 * (size_t)d) * sizeof(float);
-  if (dv > 1024 || smem > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;
+  if (dv > 1024 || d > 1024) return PE_ERR_UNSUPPORTED_SIZE;
   if (dtype != PE_F32 && dtype != PE_BF16) return PE_ERR_UNSUPPORTED_DTYPE;
   pe::DeltaArgs args{qkv, a, dt_bias, A_log, b, gate, gate_ld, norm_w, eps, q_scale, out, S, seq_slot, seq_qstart,
-                     n_seqs, heads, kv_heads, d, dv, n_slots, status};
-  const int widest = dv > d ? dv : d;
-  const int threads = (widest + 31) / 32 * 32 > 1024 ? 1024 : (widest + 31) / 32 * 32;
-  auto kernel = dtype == PE_F32 ? pe::delta_rule_kernel<float> : pe::delta_rule_kernel<__nv_bfloat16>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+                     n_seqs, heads, kv_heads, d, dv, n_slots, 0, 1, nullptr, status};
+  if (chunk > 0) {
+    if (!scratch || max_chunks <= 0 || (long long)max_chunks * chunk < max_q || max_chunks > 32767) return PE_ERR_BAD_ARGUMENT;
+    args.chunk = chunk; args.max_chunks = max_chunks; args.scratch = scratch;
   }
-  pe::launch(kernel, dim3(heads, n_seqs), dim3(threads), smem, stream, args);
+  const int widest = dv > d ? dv : d;
+  const int reg = (d <= 32 && widest <= 512) ? 32 : (d <= 64 && widest <= 256 ? 64 : (d <= 128 && widest <= 256 ? 128 : 0));
+  if (reg == 0 && ((size_t)d * widest + 3 * (size_t)d) * sizeof(float) > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;
+  int rc;
+#define PE_DELTA(T)                                                       \
+  (reg == 32 ? pe::delta_run<T, 32>(args, stream)                         \
+   : reg == 64 ? pe::delta_run<T, 64>(args, stream)                       \
+   : reg == 128 ? pe::delta_run<T, 128>(args, stream) : pe::delta_run<T, 0>(args, stream))
+  rc = dtype == PE_F32 ? PE_DELTA(float) : PE_DELTA(__nv_bfloat16);
+#undef PE_DELTA
+  if (rc != PE_OK) return rc;
   PE_LAUNCH_CHECK();
   return PE_OK;
 }

@@ -76,9 +76,9 @@ _SIGNATURES = {
     "pe_attention_decode_noalloc": [I, P, L, P, L, I, I, I, I, F, I, P, P, P, P, I, I, P, P, I, I, P, P],
     "pe_embed_pair_gather": [I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
     "pe_rmsnorm_residual_sum": [I, P, P, P, I, P, P, P, I, I, F, P],
-    "pe_mlstm_recurrence": [I, P, P, P, P, L, P, P, P, F, F, F, P, P, P, P, P, P, I, I, I, I, I, P, P],
+    "pe_mlstm_recurrence": [I, P, P, P, P, L, P, P, P, F, F, F, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, P],
     "pe_short_conv_silu": [I, P, L, I, P, I, P, P, P, P, P, I, I, I, I, P, P],
-    "pe_delta_rule_recurrence": [I, P, P, P, P, P, P, L, P, F, F, P, P, P, P, I, I, I, I, I, I, P, P],
+    "pe_delta_rule_recurrence": [I, P, P, P, P, P, P, L, P, F, F, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, P],
     "pe_moe_route": [P, P, I, I, I, P, P, P],
     "pe_moe_group": [P, I, I, I, P, P, P, P],
     "pe_moe_rows_gemm": [I, I, P, L, P, P, I, I, P, L, P, L, I, I, I, F, F, P],
@@ -88,6 +88,8 @@ _SIGNATURES = {
 _RESTYPES = {"pe_wait_limit_polls": (L, []),
              "pe_attention_generic_scratch_floats": (L, [I, I, I, I]),
              "pe_wkv_scratch_floats": (L, [I, I, I, I]),
+             "pe_mlstm_scratch_floats": (L, [I, I, I, I, I]),
+             "pe_delta_rule_scratch_floats": (L, [I, I, I, I, I]),
              "pe_sample_scratch_bytes": (L, [I, I, F, I, F, F])}
 
 

@@ -597,18 +597,24 @@ def rmsnorm_residual_sum(residual: torch.Tensor, deltas, scales, weight: torch.T
 # ---- recurrences ------------------------------------------------------------------------------------------------------
 def mlstm_recurrence(q, k, v, g, gates: torch.Tensor, gate_bias: torch.Tensor, norm_w: torch.Tensor, cap: float, eps: float,
                      q_scale: float, out: torch.Tensor, S: torch.Tensor, n: torch.Tensor, m: torch.Tensor,
-                     seq_slot: torch.Tensor, seq_qstart: torch.Tensor, n_seqs: int, heads: int, d: int, dv: int,
-                     status: torch.Tensor) -> None:
-    """csrc/mlstm.cu.  ``q, k, v, g``: views of one row stride in the run dtype; ``gates [N, 2 * heads]`` float32."""
+                     seq_slot: torch.Tensor, seq_qstart: torch.Tensor, n_seqs: int, max_q: int, heads: int, d: int, dv: int,
+                     status: torch.Tensor, chunk: int = 0, max_chunks: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
+    """csrc/mlstm.cu.  ``q, k, v, g``: views of one row stride in the run dtype; ``gates [N, 2 * heads]`` float32.
+    ``chunk`` > 0: prompts cut into chunks of that many tokens that run side by side (``scratch``: float32,
+    ``mlstm_scratch_floats`` of them)."""
     ld = q.stride(0)
     _need(all(t.stride(0) == ld and t.stride(1) == 1 and t.dtype == q.dtype for t in (k, v, g)), "mlstm: q, k, v, g share a row stride")
     _need(gates.dtype == torch.float32 and gates.is_contiguous() and S.dtype == torch.float32 and S.is_contiguous()
           and n.is_contiguous() and m.is_contiguous() and out.is_contiguous() and out.dtype == q.dtype, "mlstm: layouts")
     check(library().pe_mlstm_recurrence(dtype_tag(q.dtype), _ptr(q), _ptr(k), _ptr(v), _ptr(g), ld, _ptr(gates), _ptr(gate_bias),
                                         _ptr(norm_w), float(cap), float(eps), float(q_scale), _ptr(out), _ptr(S), _ptr(n), _ptr(m),
-                                        _ptr(seq_slot), _ptr(seq_qstart), n_seqs, heads, d, dv, S.shape[0], _ptr(status),
-                                        _stream()), "mlstm_recurrence")
-    _count(1)
+                                        _ptr(seq_slot), _ptr(seq_qstart), n_seqs, int(max_q), heads, d, dv, S.shape[0], int(chunk),
+                                        int(max_chunks), _ptr(scratch), _ptr(status), _stream()), "mlstm_recurrence")
+    _count(3 if chunk > 0 else 1)
+
+
+def mlstm_scratch_floats(n_seqs: int, heads: int, d: int, dv: int, max_chunks: int) -> int:
+    return int(library().pe_mlstm_scratch_floats(n_seqs, heads, d, dv, max_chunks))
 
 
 def short_conv_silu(x: torch.Tensor, col0: int, w: torch.Tensor, tail: torch.Tensor, token_seq: torch.Tensor,
@@ -621,24 +627,31 @@ def short_conv_silu(x: torch.Tensor, col0: int, w: torch.Tensor, tail: torch.Ten
     _need(taps == 1 or tuple(tail.shape[1:]) == (taps - 1, channels), "short_conv: tail shape")
     check(library().pe_short_conv_silu(dtype_tag(x.dtype), _ptr(x), x.stride(0), int(col0), _ptr(w), taps, _ptr(tail),
                                        _ptr(token_seq), _ptr(seq_slot), _ptr(seq_qstart), _ptr(out), x.shape[0], n_seqs, channels,
-                                       tail.shape[0], _ptr(status), _stream()), "short_conv_silu")
+                                       tail.shape[0] if taps > 1 else (1 << 30), _ptr(status), _stream()), "short_conv_silu")
     _count(2 if taps > 1 else 1)
 
 
 def delta_rule_recurrence(qkv: torch.Tensor, a: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, b: torch.Tensor,
                           gate: torch.Tensor, norm_w: torch.Tensor, eps: float, q_scale: float, out: torch.Tensor,
-                          S: torch.Tensor, seq_slot: torch.Tensor, seq_qstart: torch.Tensor, n_seqs: int, heads: int,
-                          kv_heads: int, d: int, dv: int, status: torch.Tensor) -> None:
+                          S: torch.Tensor, seq_slot: torch.Tensor, seq_qstart: torch.Tensor, n_seqs: int, max_q: int, heads: int,
+                          kv_heads: int, d: int, dv: int, status: torch.Tensor, chunk: int = 0, max_chunks: int = 1,
+                          scratch: Optional[torch.Tensor] = None) -> None:
     """csrc/delta_rule.cu.  ``qkv [N, 2 * kv_heads * d + heads * dv]`` after the convolutions; ``a [N, heads * d]`` and
-    ``b [N, heads]`` float32; ``gate [N, heads * dv]`` in the run dtype (any row stride)."""
+    ``b [N, heads]`` float32; ``gate [N, heads * dv]`` in the run dtype (any row stride).  ``chunk`` > 0: prompts cut into
+    chunks of that many tokens that run side by side (``scratch``: float32, ``delta_rule_scratch_floats`` of them)."""
     _need(qkv.is_contiguous() and qkv.shape[1] == 2 * kv_heads * d + heads * dv, "delta_rule: q|k|v layout")
     _need(a.dtype == torch.float32 and a.is_contiguous() and b.dtype == torch.float32 and b.is_contiguous(), "delta_rule: a, b f32")
     _need(gate.stride(1) == 1 and gate.dtype == qkv.dtype and out.is_contiguous() and S.is_contiguous(), "delta_rule: layouts")
     check(library().pe_delta_rule_recurrence(dtype_tag(qkv.dtype), _ptr(qkv), _ptr(a), _ptr(dt_bias), _ptr(A_log), _ptr(b),
                                              _ptr(gate), gate.stride(0), _ptr(norm_w), float(eps), float(q_scale), _ptr(out),
-                                             _ptr(S), _ptr(seq_slot), _ptr(seq_qstart), n_seqs, heads, kv_heads, d, dv,
-                                             S.shape[0], _ptr(status), _stream()), "delta_rule_recurrence")
-    _count(1)
+                                             _ptr(S), _ptr(seq_slot), _ptr(seq_qstart), n_seqs, int(max_q), heads, kv_heads, d, dv,
+                                             S.shape[0], int(chunk), int(max_chunks), _ptr(scratch), _ptr(status), _stream()),
+          "delta_rule_recurrence")
+    _count(3 if chunk > 0 else 1)
+
+
+def delta_rule_scratch_floats(n_seqs: int, heads: int, d: int, dv: int, max_chunks: int) -> int:
+    return int(library().pe_delta_rule_scratch_floats(n_seqs, heads, d, dv, max_chunks))
 
 
 # ---- routed experts ---------------------------------------------------------------------------------------------------

@@ -26,6 +26,11 @@ from .registry import register
 from .spec import CacheRequest, WeightDecl
 
 
+# tokens per chunk when a prompt is cut into chunks that run side by side; steps whose longest sequence has no more
+# tokens than two chunks walk each sequence in one go
+CHUNK_TOKENS = 64
+
+
 @register("mixer", "gated_delta")
 class GatedDeltaMixer:
     """params: ``hidden``, ``n_heads``, ``n_kv_heads``, ``head_dim``, ``v_head_dim``, ``conv`` (taps), ``eps`` (of the
@@ -68,8 +73,10 @@ class GatedDeltaMixer:
         self.v_dim = int(params["v_head_dim"])
         self.taps = int(params["conv"])
         self.eps = float(params.get("eps", 1e-5))
-        if self.v_dim > 1024 or (self.head_dim * self.v_dim + 3 * self.head_dim) * 4 > 200 * 1024:
-            raise ValueError(f"a head of {self.head_dim} x {self.v_dim} is beyond what the recurrence kernel keeps in shared memory")
+        d, dv = self.head_dim, self.v_dim
+        in_registers = (d <= 32 and dv <= 512) or (d <= 128 and dv <= 256)
+        if max(d, dv) > 1024 or (not in_registers and (d * max(d, dv) + 3 * d) * 4 > 200 * 1024) or (d * (d + 1) + 8 * d) * 4 > 200 * 1024:
+            raise ValueError(f"a head of {d} x {dv} is beyond what the recurrence kernels keep on chip")
         f32 = torch.float32
         self.rank_a, self.rank_g = int(weights["a1"].shape[0]), int(weights["g1"].shape[0])
         if weights["a2"].shape[1] != self.rank_a or weights["g2"].shape[1] != self.rank_g:
@@ -113,9 +120,15 @@ class GatedDeltaMixer:
         gate = ctx.buffer("delta.gate", (n, self.n_heads * self.v_dim), rt.dtype)
         rt.linear(low_g, self.g2, out=gate)
         out = ctx.buffer("delta.out", (n, self.n_heads * self.v_dim), rt.dtype)
+        chunk, max_chunks, scratch = 0, 1, None
+        if ctx.max_q > 2 * CHUNK_TOKENS:
+            chunk = CHUNK_TOKENS
+            max_chunks = -(-ctx.max_q // chunk)
+            scratch = ctx.buffer("delta.scratch", (ops.delta_rule_scratch_floats(ctx.n_seqs, self.n_heads, self.head_dim, self.v_dim,
+                                                                               max_chunks),), torch.float32)
         ops.delta_rule_recurrence(qkv, decay, self.dt_bias, self.A_log, beta, gate, self.norm, self.eps, self.head_dim ** -0.5,
-                                  out, view.state("S"), ctx.seq_slot, ctx.seq_qstart, ctx.n_seqs, self.n_heads,
-                                  self.n_kv_heads, self.head_dim, self.v_dim, rt.status)
+                                  out, view.state("S"), ctx.seq_slot, ctx.seq_qstart, ctx.n_seqs, ctx.max_q, self.n_heads,
+                                  self.n_kv_heads, self.head_dim, self.v_dim, rt.status, chunk, max_chunks, scratch)
         delta = ctx.buffer("delta.delta", (n, self.hidden), rt.dtype)
         rt.linear(out, self.o_proj, out=delta)
         return delta

@@ -25,6 +25,11 @@ from .registry import register
 from .spec import CacheRequest, WeightDecl
 
 
+# tokens per chunk when a prompt is cut into chunks that run side by side; steps whose longest sequence has no more
+# tokens than two chunks walk each sequence in one go
+CHUNK_TOKENS = 64
+
+
 @register("mixer", "mlstm")
 class MlstmMixer:
     """params: ``hidden``, ``n_heads``, ``head_dim``, ``v_head_dim``, ``gate_cap``, ``eps`` (of the per-head norm).
@@ -56,8 +61,9 @@ class MlstmMixer:
         self.v_dim = int(params["v_head_dim"])
         self.cap = float(params["gate_cap"])
         self.eps = float(params.get("eps", 1e-5))
-        if self.v_dim > 1024 or (self.head_dim * self.v_dim + 3 * self.head_dim) * 4 > 200 * 1024:
-            raise ValueError(f"a head of {self.head_dim} x {self.v_dim} is beyond what the recurrence kernel keeps in shared memory")
+        in_registers = self.head_dim <= 32 or (self.head_dim <= 64 and self.v_dim <= 512) or (self.head_dim <= 128 and self.v_dim <= 256)
+        if self.v_dim > 1024 or (not in_registers and (self.head_dim * self.v_dim + 3 * self.head_dim) * 4 > 200 * 1024):
+            raise ValueError(f"a head of {self.head_dim} x {self.v_dim} is beyond what the recurrence kernel keeps on chip")
         f32 = torch.float32
         self.qkvg = fuse_rows(runtime, [weights["q_proj"], weights["k_proj"], weights["v_proj"], weights["g_proj"]])
         self.gates = fuse_rows(runtime, [weights["i_proj"], weights["f_proj"]])
@@ -79,10 +85,16 @@ class MlstmMixer:
         if y.data_ptr() != gates.data_ptr():
             gates.copy_(y)
         out = ctx.buffer("mlstm.out", (n, vv), rt.dtype)
+        chunk, max_chunks, scratch = 0, 1, None
+        if ctx.max_q > 2 * CHUNK_TOKENS:
+            chunk = CHUNK_TOKENS
+            max_chunks = -(-ctx.max_q // chunk)
+            scratch = ctx.buffer("mlstm.scratch", (ops.mlstm_scratch_floats(ctx.n_seqs, self.n_heads, self.head_dim, self.v_dim,
+                                                                          max_chunks),), torch.float32)
         ops.mlstm_recurrence(qkvg[:, :qk], qkvg[:, qk:2 * qk], qkvg[:, 2 * qk:2 * qk + vv], qkvg[:, 2 * qk + vv:], gates,
                              self.gate_bias, self.norm, self.cap, self.eps, self.head_dim ** -0.5, out, view.state("S"),
-                             view.state("n"), view.state("m"), ctx.seq_slot, ctx.seq_qstart, ctx.n_seqs, self.n_heads,
-                             self.head_dim, self.v_dim, rt.status)
+                             view.state("n"), view.state("m"), ctx.seq_slot, ctx.seq_qstart, ctx.n_seqs, ctx.max_q, self.n_heads,
+                             self.head_dim, self.v_dim, rt.status, chunk, max_chunks, scratch)
         delta = ctx.buffer("mlstm.delta", (n, self.hidden), rt.dtype)
         rt.linear(out, self.o_proj, out=delta)
         return delta
