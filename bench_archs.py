@@ -1,4 +1,5 @@
-"""``python bench.py --archs``: the Vabelorn architecture beside the Qwen3 dense decoder at equal layer sizes.
+"""``python bench.py --archs``: the Vabelorn and Lunadra architectures beside the Qwen3 dense decoder at equal layer sizes
+(``--arch-names`` picks among them; Lunadra's own kernels stand beside the like kernels of the Vabelorn path).
 
 Random weights, bfloat16, one B200.  For each size: tokens/s of a 2,048-token prompt and of decode steps at batch 8
 (context 2,048) through ``ModelRunner.step``, for both architectures; then the kernels that only the new
@@ -30,6 +31,24 @@ def vabelorn_config(pe, s):
     return pe.VabelornConfig.from_dict({"architecture": "Vabelorn", "vocab": s["vocab"], "width": s["width"], "logit_scale": 1.0,
                                         "norm": {"eps": 1e-6}, "token_side": {"dim": 64},
                                         "layers": [att if i % 2 == 0 else wkv for i in range(s["layers"])]})
+
+
+def lunadra_config(pe, s):
+    """Lunadra at the same width, attention heads, feed-forward and vocabulary: window attention beside a gated delta rule
+    (its state as large as the wkv layer's), mlstm layers, a dense feed-forward and routed experts whose two chosen
+    experts and shared expert together are as wide as the dense one."""
+    side = {"type": "parallel",
+            "mixer": {"left": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+                               "scale": 1.0 / math.sqrt(s["dim"]), "mask": {"size": 1024}, "rot": {"base": 1e6, "dims": s["dim"] // 2}},
+                      "right": {"heads": s["wkv_heads"] // 4, "kv_heads": s["wkv_heads"] // 8, "dim": 128, "vdim": 128, "conv": 4, "rank": 64},
+                      "left_scale": 1.0, "right_scale": 1.0},
+            "mlp": {"kind": "dense", "ff": s["ff"]}}
+    mem = {"type": "mlstm", "mixer": {"heads": s["width"] // 256, "dim": 128, "vdim": 256, "gate_cap": 15.0},
+           "mlp": {"kind": "moe", "router": {"experts": 8, "identity": 2, "top": 2}, "expert": {"ff": s["ff"] // 4, "limit": 7.0},
+                   "shared": {"ff": s["ff"] // 2, "limit": 7.0}}}
+    return pe.LunadraConfig.from_dict({"architecture": "Lunadra", "vocab": s["vocab"], "width": s["width"], "residual_mult": 1.0,
+                                       "norm": {"eps": 1e-6}, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+                                       "layers": [side if i % 2 == 0 else mem for i in range(s["layers"])]})
 
 
 def qwen3_config(pe, s):
@@ -230,6 +249,156 @@ def kernel_pairs(pe, torch, s, hbm_gbs, prompt, batch, context):
     return out
 
 
+FP32_TFLOPS = 148 * 128 * 2 * 1.9e9 / 1e12      # float32 multiply-adds of the CUDA cores, for the recurrences' rooflines
+
+
+def lunadra_kernel_pairs(pe, torch, s, hbm_gbs, prompt, batch, context):
+    """The kernels that only Lunadra has, each beside the like kernel of the Vabelorn path at the same shape.  A kernel's
+    roofline time is the larger of its bytes over the copy bandwidth and its float32 operations over the CUDA cores'
+    rate; ``times_as_far_from_roofline`` divides the new kernel's distance from its roofline by the like kernel's."""
+    ops = pe.kernels.ops
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    width = s["width"]
+    flush = torch.zeros(96 * 2 ** 20, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    out = {}
+
+    def us_of(fn):
+        return 1e3 * timed(torch, fn, 20, 5, flush, graph=True)
+
+    def roof_us(nbytes, flops=0.0):
+        return max(nbytes / (hbm_gbs * 1e9), flops / (FP32_TFLOPS * 1e12)) * 1e6
+
+    def entry(name, us_new, roof_new, like, us_like, roof_like):
+        out[name] = {"us": round(us_new, 2), "roofline_us": round(roof_new, 2), "of_roofline": round(roof_new / us_new, 3)}
+        if like:
+            out[name].update({"like_kernel": like, "like_us": round(us_like, 2), "like_of_roofline": round(roof_like / us_like, 3),
+                              "times_as_far_from_roofline": round((us_new / roof_new) / (us_like / roof_like), 2)})
+
+    for what, n_seqs, q_len in (("prompt", 1, prompt), ("decode", batch, 1)):
+        n = n_seqs * q_len
+        qstart = torch.arange(0, n + 1, q_len, dtype=torch.int32, device=dev)
+        slots = torch.arange(n_seqs, dtype=torch.int32, device=dev)
+        token_seq = torch.arange(n_seqs, dtype=torch.int32, device=dev).repeat_interleave(q_len).contiguous()
+        token_pos = torch.arange(q_len, dtype=torch.int32, device=dev).repeat(n_seqs).contiguous() + (0 if q_len > 1 else 5)
+        chunked = q_len > 128
+        max_chunks = -(-q_len // 64) if chunked else 1
+        # the like kernel: the wkv recurrence at its own shape (state heads x 64 x 64)
+        WH, wd = s["wkv_heads"], s["wkv_dim"]
+        hd = WH * wd
+        r, k, v, g = (torch.randn(n, hd, device=dev).to(bf) for _ in range(4))
+        k.mul_(0.3)
+        wlin = torch.randn(n, hd, device=dev)
+        w0, u, gn = torch.zeros(hd, device=dev), torch.zeros(hd, device=dev), torch.ones(hd, device=dev)
+        res = torch.empty(n, hd, dtype=bf, device=dev)
+        state = torch.zeros(n_seqs, WH, wd, wd, device=dev)
+        prev = torch.zeros(n_seqs, width, device=dev)
+        x = torch.randn(n, width, device=dev).to(bf)
+        scratch = torch.empty(ops.wkv_scratch_floats(n_seqs, WH, wd, max_chunks), device=dev) if chunked else None
+        us_wkv = us_of(lambda: ops.wkv_recurrence(r, k, v, g, wlin, w0, u, gn, 1e-6, res, state, prev, x, slots, qstart, n_seqs, q_len,
+                                                  WH, wd, 64 if chunked else 0, max_chunks, scratch, status))
+        roof_wkv = roof_us(n * hd * (4 * 2 + 4 + 2) + n_seqs * WH * wd * wd * 8, n * WH * wd * wd * 5.0)
+        # mlstm
+        H, d, dv = width // 256, 128, 256
+        qk, vv = H * d, H * dv
+        qkvg = (torch.randn(n, 2 * qk + 2 * vv, device=dev) * 0.5).to(bf)
+        gates = torch.randn(n, 2 * H, device=dev)
+        gbias, nw = torch.zeros(2 * H, device=dev), torch.ones(vv, device=dev)
+        o = torch.empty(n, vv, dtype=bf, device=dev)
+        S, nn, mm = torch.zeros(n_seqs, H, d, dv, device=dev), torch.zeros(n_seqs, H, d, device=dev), torch.zeros(n_seqs, H, device=dev)
+        scratch_m = torch.empty(ops.mlstm_scratch_floats(n_seqs, H, d, dv, max_chunks), device=dev) if chunked else None
+        us = us_of(lambda: ops.mlstm_recurrence(qkvg[:, :qk], qkvg[:, qk:2 * qk], qkvg[:, 2 * qk:2 * qk + vv], qkvg[:, 2 * qk + vv:], gates,
+                                                gbias, nw, 15.0, 1e-6, d ** -0.5, o, S, nn, mm, slots, qstart, n_seqs, q_len, H, d, dv,
+                                                status, 64 if chunked else 0, max_chunks, scratch_m))
+        entry(f"{what}: mlstm recurrence, head norm, gate", us, roof_us(n * (2 * qk + 3 * vv) * 2 + n_seqs * H * d * dv * 8, n * H * d * dv * 5.0),
+              "wkv_recurrence", us_wkv, roof_wkv)
+        # gated delta rule
+        DH, DG, dd, ddv = s["wkv_heads"] // 4, s["wkv_heads"] // 8, 128, 128
+        ch = 2 * DG * dd + DH * ddv
+        qkv = (torch.randn(n, ch, device=dev) * 0.5).to(bf)
+        a_lin, beta = torch.randn(n, DH * dd, device=dev), torch.randn(n, DH, device=dev)
+        dtb, alog, nw2 = torch.zeros(DH * dd, device=dev), torch.zeros(DH, device=dev), torch.ones(ddv, device=dev)
+        gate = torch.randn(n, DH * ddv, device=dev).to(bf)
+        o2 = torch.empty(n, DH * ddv, dtype=bf, device=dev)
+        S2 = torch.zeros(n_seqs, DH, dd, ddv, device=dev)
+        scratch_d = torch.empty(ops.delta_rule_scratch_floats(n_seqs, DH, dd, ddv, max_chunks), device=dev) if chunked else None
+        us = us_of(lambda: ops.delta_rule_recurrence(qkv, a_lin, dtb, alog, beta, gate, nw2, 1e-6, dd ** -0.5, o2, S2, slots, qstart, n_seqs,
+                                                     q_len, DH, DG, dd, ddv, status, 64 if chunked else 0, max_chunks, scratch_d))
+        entry(f"{what}: gated delta recurrence, head norm, gate", us,
+              roof_us(n * (ch * 2 + DH * dd * 4 + DH * ddv * 4) + n_seqs * DH * dd * ddv * 8, n * DH * dd * ddv * 7.0),
+              "wkv_recurrence", us_wkv, roof_wkv)
+        # short convolutions beside the token shift (both: a token's row with the rows before it, kept inputs at the start)
+        wide = torch.randn(n, ch + 128, device=dev).to(bf)
+        cw = torch.randn(ch, 4, device=dev)
+        tail = torch.zeros(n_seqs, 3, ch, device=dev)
+        co = torch.empty(n, ch, dtype=bf, device=dev)
+        us = us_of(lambda: ops.short_conv_silu(wide, 0, cw, tail, token_seq, slots, qstart, co, n_seqs, status))
+        mixes = torch.empty(5, n, width, dtype=bf, device=dev)
+        mu = torch.rand(5, width, device=dev)
+        us_like = us_of(lambda: ops.token_shift_mix(x, mu, prev, token_seq, slots, qstart, mixes, status))
+        entry(f"{what}: short convolutions, silu, kept inputs", us, roof_us(n * ch * 4), "token_shift_mix", us_like, roof_us(n * width * 12))
+        # the add of three scaled outputs in the norm beside the add of one
+        stream = torch.randn(n, width, device=dev)
+        deltas = [torch.randn(n, width, device=dev).to(bf) for _ in range(3)]
+        w = torch.ones(width, device=dev)
+        normed = torch.empty(n, width, dtype=bf, device=dev)
+        us = us_of(lambda: ops.rmsnorm_residual_sum(stream, deltas, [1.0, 0.5, 0.7], w, normed, 1e-6))
+        us_like = us_of(lambda: ops.rmsnorm_residual(stream, deltas[0], w, normed, 1e-6))
+        entry(f"{what}: add of three scaled outputs, norm", us, roof_us(n * width * (8 + 6 + 2)), "rmsnorm_residual", us_like,
+              roof_us(n * width * (8 + 2 + 2)))
+        # embedding with the pair table beside the plain gather
+        table = torch.randn(s["vocab"], width, device=dev).to(bf)
+        pairs = torch.randn(65522, width, device=dev).to(bf)
+        ids = torch.randint(0, s["vocab"], (n,), dtype=torch.int32, device=dev)
+        last = torch.zeros(n_seqs, dtype=torch.int32, device=dev)
+        emb = torch.empty(n, width, device=dev)
+        us = us_of(lambda: ops.embed_pair_gather(table, pairs, ids, token_seq, token_pos, slots, qstart, last, emb, 65521, 31, 7, status))
+        us_like = us_of(lambda: ops.embed_gather(table, ids, emb, status))
+        entry(f"{what}: token and pair embedding", us, roof_us(n * width * 8), "embed_gather", us_like, roof_us(n * width * 6))
+        # routed experts: routing and grouping, then the experts' products
+        E, top, ff = 8, 2, s["ff"] // 4
+        logits = torch.randn(n, E + 2, device=dev)
+        corr = torch.zeros(E + 2, device=dev)
+        chosen = torch.empty(n, top, dtype=torch.int32, device=dev)
+        weight = torch.empty(n, top, device=dev)
+        offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        row_token = torch.empty(n * top, dtype=torch.int32, device=dev)
+        pair_row = torch.empty(n, top, dtype=torch.int32, device=dev)
+
+        def route():
+            ops.moe_route(logits, corr, top, chosen, weight)
+            ops.moe_group(chosen, n, top, E, offsets, row_token, pair_row)
+        entry(f"{what}: router softmax, choice, grouping (2 kernels)", us_of(route), roof_us(n * (E + 2) * 4 + n * top * 16), None, 0, 0)
+        gate_up = (torch.randn(E, 2 * ff, width, device=dev) * 0.02).to(bf)
+        act = torch.empty(n * top, ff, dtype=bf, device=dev)
+        route()
+        if what == "decode":
+            us = us_of(lambda: ops.moe_rows_gemm(x, row_token, offsets, E, n * top, gate_up, act, 3, 7.0, 1.702))
+            dense = (torch.randn(E * 2 * ff, width, device=dev) * 0.02).to(bf)
+            act2 = torch.empty(n, E * ff, dtype=bf, device=dev)
+            us_like = us_of(lambda: ops.gemm_smallm(x, dense, act2, pair_offset=E * ff))
+            nbytes = E * 2 * ff * width * 2
+            entry("decode: experts' gate|up product with activation (every expert's weights once)", us, roof_us(nbytes),
+                  "gemm_smallm with SiLU epilogue, same bytes", us_like, roof_us(nbytes))
+        else:
+            xs = torch.empty(n * top, width, dtype=bf, device=dev)
+
+            def experts():
+                ops.moe_gather_rows(x, row_token, offsets, E, xs)
+                gu = torch._grouped_mm(xs, gate_up.transpose(1, 2), offs=offsets[1:], out_dtype=bf)
+                ops.glu_act(gu, act, "clamped_swish", 7.0, 1.702)
+            us = us_of(experts)
+            out["prompt: experts' rows gathered, library product over row groups, activation"] = {
+                "us": round(us, 2), "tflops": round(2.0 * n * top * 0.8 * 2 * ff * width / us / 1e6, 1), "like_kernel": "library product"}
+        rows = torch.randn(n * top, width, device=dev).to(bf)
+        shared = torch.randn(n, width, device=dev).to(bf)
+        y = torch.empty(n, width, dtype=bf, device=dev)
+        us = us_of(lambda: ops.moe_combine(rows, x, shared, pair_row, weight, top, y))
+        entry(f"{what}: weighted sum of the chosen experts and the shared one", us, roof_us(n * width * 2 * (top + 3)), None, 0, 0)
+    return out
+
+
 def main(args):
     import torch
 
@@ -239,19 +408,27 @@ def main(args):
     pe = importlib.import_module("pytorch-engine_b200")
     peaks = bench.load_peaks()
     prompt, batch, context = args.prefill_tokens, args.batch, min(args.context, 2048)
-    result = {"metric": "vabelorn_beside_qwen3", "dtype": "bf16", "data": "synthetic (random weights)", "peaks": peaks,
+    result = {"metric": "architectures_beside_qwen3", "dtype": "bf16", "data": "synthetic (random weights)", "peaks": peaks,
               "prompt_tokens": prompt, "decode_batch": batch, "decode_context": context,
               "flush": "model runs: weights larger than L2; kernel pairs: 384 MB written between iterations", "sizes": {}}
     names = [n for n in SIZES if not args.arch_sizes or n in args.arch_sizes.split(",")]
     for name in names:
         s = SIZES[name]
         row = {"shape": s}
-        for arch, cfg in (("vabelorn", vabelorn_config(pe, s)), ("qwen3", qwen3_config(pe, s))):
-            row[arch] = model_speeds(pe, torch, cfg, prompt, batch, context, args.steps, max(args.warmup, 3))
+        wanted = [a for a in (args.arch_names or "vabelorn,qwen3,lunadra").split(",") if a]
+        for arch, make in (("vabelorn", vabelorn_config), ("qwen3", qwen3_config), ("lunadra", lunadra_config)):
+            if arch not in wanted:
+                continue
+            row[arch] = model_speeds(pe, torch, make(pe, s), prompt, batch, context, args.steps, max(args.warmup, 3))
             print(f"[{name}] {arch}: {row[arch]}", file=sys.stderr, flush=True)
-        row["kernels"] = kernel_pairs(pe, torch, s, peaks["hbm_gbs"], prompt, batch, context)
-        for k, v in row["kernels"].items():
-            print(f"[{name}] {k}: {v}", file=sys.stderr, flush=True)
+        if "vabelorn" in wanted:
+            row["kernels"] = kernel_pairs(pe, torch, s, peaks["hbm_gbs"], prompt, batch, context)
+            for k, v in row["kernels"].items():
+                print(f"[{name}] {k}: {v}", file=sys.stderr, flush=True)
+        if "lunadra" in wanted:
+            row["lunadra_kernels"] = lunadra_kernel_pairs(pe, torch, s, peaks["hbm_gbs"], prompt, batch, context)
+            for k, v in row["lunadra_kernels"].items():
+                print(f"[{name}] {k}: {v}", file=sys.stderr, flush=True)
         result["sizes"][name] = row
     result["gpu_launches"] = pe.kernels.ops.launch_count()
     print(json.dumps(result))

@@ -163,6 +163,8 @@ int pe_moe_group(const int* chosen, int n_tokens, int top, int n_real, int* offs
 int pe_moe_rows_gemm(int dtype, int out_dtype, const void* x, long long x_ld, const int* row_map, const int* offsets,
     int n_groups, int max_rows, const void* w, long long w_group_stride, void* out, long long out_ld, int n_out, int k_dim,
     int glu, float limit, float alpha, cudaStream_t stream);
+int pe_moe_gather_rows(int dtype, const void* x, const int* row_token, const int* offsets, int n_groups, void* xs,
+    int max_rows, int width, cudaStream_t stream);
 int pe_moe_combine(int dtype, const void* rows, const void* x, const void* shared, const int* pair_row,
     const float* weight, int top, void* out, int n_tokens, int width, cudaStream_t stream);
 int pe_glu_act(int dtype, const void* gate_up, void* out, int n_rows, int inter, int kind, float limit, float alpha,

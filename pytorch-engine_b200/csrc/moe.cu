@@ -223,6 +223,25 @@ __global__ void __launch_bounds__(256) moe_rows_gemm_kernel(const T* x, long lon
   }
 }
 
+// xs[r] = x[row_token[r]] for the rows that some expert owns (r < offsets[n_groups]): the grouped rows laid out for a
+// library product over row groups.
+template <typename T>
+__global__ void moe_gather_kernel(const T* x, const int* row_token, const int* offsets, int n_groups, T* __restrict__ xs,
+                                  int max_rows, int width) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  if (r >= max_rows || r >= offsets[n_groups]) return;
+  const T* src = x + (size_t)row_token[r] * width;
+  T* dst = xs + (size_t)r * width;
+  if (sizeof(T) == 2 && width % 8 == 0) {
+    for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8)
+      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
+  } else {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
+  }
+}
+
 // y[t][c] = sum_j weight[t][j] * (rows[pair_row[t][j]][c] or x[t][c]) (+ shared[t][c])
 template <typename T>
 __global__ void moe_combine_kernel(const T* rows, const T* x, const T* shared, const int* pair_row, const float* weight,
@@ -312,6 +331,24 @@ extern "C" int pe_moe_rows_gemm(int dtype, int out_dtype, const void* x, long lo
   else if (dtype == PE_BF16 && out_dtype == PE_F32) PE_MOE_LAUNCH(__nv_bfloat16, float);
   else return PE_ERR_UNSUPPORTED_DTYPE;
 #undef PE_MOE_LAUNCH
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}
+
+extern "C" int pe_moe_gather_rows(int dtype, const void* x, const int* row_token, const int* offsets, int n_groups, void* xs,
+                                  int max_rows, int width, cudaStream_t stream) {
+  if (max_rows <= 0) return PE_OK;
+  if (width <= 0 || n_groups <= 0) return PE_ERR_BAD_ARGUMENT;
+  if (((uintptr_t)x % 16) || ((uintptr_t)xs % 16)) return PE_ERR_BAD_ARGUMENT;
+  const int threads = width >= 2048 ? 256 : 128;
+  if (dtype == PE_F32)
+    pe::launch(pe::moe_gather_kernel<float>, max_rows, threads, 0, stream, (const float*)x, row_token, offsets, n_groups, (float*)xs,
+               max_rows, width);
+  else if (dtype == PE_BF16)
+    pe::launch(pe::moe_gather_kernel<__nv_bfloat16>, max_rows, threads, 0, stream, (const __nv_bfloat16*)x, row_token, offsets,
+               n_groups, (__nv_bfloat16*)xs, max_rows, width);
+  else
+    return PE_ERR_UNSUPPORTED_DTYPE;
   PE_LAUNCH_CHECK();
   return PE_OK;
 }

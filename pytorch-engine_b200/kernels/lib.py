@@ -82,6 +82,7 @@ _SIGNATURES = {
     "pe_moe_route": [P, P, I, I, I, P, P, P],
     "pe_moe_group": [P, I, I, I, P, P, P, P],
     "pe_moe_rows_gemm": [I, I, P, L, P, P, I, I, P, L, P, L, I, I, I, F, F, P],
+    "pe_moe_gather_rows": [I, P, P, P, I, P, I, I, P],
     "pe_moe_combine": [I, P, P, P, P, P, I, P, I, I, P],
     "pe_glu_act": [I, P, P, I, I, I, F, F, P],
 }

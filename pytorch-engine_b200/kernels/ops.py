@@ -687,6 +687,14 @@ def moe_rows_gemm(x: torch.Tensor, row_map: Optional[torch.Tensor], offsets: tor
     _count(1)
 
 
+def moe_gather_rows(x: torch.Tensor, row_token: torch.Tensor, offsets: torch.Tensor, n_groups: int, xs: torch.Tensor) -> None:
+    """``xs[r] = x[row_token[r]]`` for the rows below ``offsets[n_groups]`` (the rest of ``xs`` is left as it is)."""
+    _need(x.is_contiguous() and xs.is_contiguous() and xs.dtype == x.dtype and xs.shape[1] == x.shape[1], "moe_gather_rows: layouts")
+    check(library().pe_moe_gather_rows(dtype_tag(x.dtype), _ptr(x), _ptr(row_token), _ptr(offsets), int(n_groups), _ptr(xs),
+                                       xs.shape[0], x.shape[1], _stream()), "moe_gather_rows")
+    _count(1)
+
+
 def moe_combine(rows: torch.Tensor, x: torch.Tensor, shared: Optional[torch.Tensor], pair_row: torch.Tensor, weight: torch.Tensor,
                 top: int, out: torch.Tensor) -> None:
     _need(x.is_contiguous() and out.is_contiguous() and rows.is_contiguous() and rows.shape[1] == x.shape[1], "moe_combine: layouts")

@@ -7,7 +7,10 @@ that return their input, optionally with a shared expert that every token passes
     expert(h) = D act(G h, U h)  with the activations of ``parts/swiglu.py``
 
 The (token, choice) pairs are grouped by expert on the device and every expert's rows go through its matrices in one
-launch per product, so nothing is read back to the host and a decode step stays recordable.
+launch per product, so nothing is read back to the host and a decode step stays recordable.  A handful of pairs (a
+decode step) and every float32 run use the package's own kernel, which streams an expert's weights once per eight
+rows; many bfloat16 rows go through the library's product over row groups (``torch._grouped_mm`` with the groups' ends
+on the device), as the other many-row products of this package that no kernel of its own takes go to the library.
 """
 from __future__ import annotations
 
@@ -19,6 +22,11 @@ from ..kernels import ops
 from .registry import register
 from .spec import WeightDecl
 from .swiglu import SwiGLU
+
+
+# (token, choice) pairs up to which the package's own row-group kernel runs (it streams an expert's weights once per
+# eight rows); beyond it, in bfloat16, the library's product over row groups
+LIBRARY_ROWS = 64
 
 
 @register("feed_forward", "routed_experts")
@@ -63,6 +71,9 @@ class RoutedExperts:
             self.gate_up = torch.stack([torch.cat([weights[f"e{e}.gate"], weights[f"e{e}.up"]]).to(device=dev, dtype=dt)
                                         for e in range(self.n_experts)]).contiguous()
             self.down = torch.stack([weights[f"e{e}.down"].to(device=dev, dtype=dt) for e in range(self.n_experts)]).contiguous()
+        # the library's product over row groups takes bfloat16 rows that start on 16-byte boundaries
+        self.library_product = (runtime.dtype == torch.bfloat16 and hasattr(torch, "_grouped_mm") and self.hidden % 8 == 0
+                                and self.intermediate % 8 == 0)
         self.shared = None
         if params.get("shared"):
             sp = dict(params["shared"])
@@ -86,7 +97,16 @@ class RoutedExperts:
         pair_row = ctx.buffer("moe.pair_row", (n, top), torch.int32)
         ops.moe_group(chosen, n, top, self.n_experts, offsets, row_token, pair_row)
         rows = ctx.buffer("moe.rows", (n * top, self.hidden), rt.dtype)
-        if self.n_experts:
+        if self.n_experts and self.library_product and n * top > LIBRARY_ROWS and rt.gemm_backend is None:
+            # many rows: the rows in expert order, then the library's product over row groups (bfloat16, float32 sums)
+            xs = ctx.buffer("moe.xs", (n * top, self.hidden), rt.dtype)
+            ops.moe_gather_rows(x, row_token, offsets, self.n_experts, xs)
+            ends = offsets[1:]
+            gu = torch._grouped_mm(xs, self.gate_up.transpose(1, 2), offs=ends, out_dtype=rt.dtype)
+            act = ctx.buffer("moe.act", (n * top, self.intermediate), rt.dtype)
+            ops.glu_act(gu, act, self.activation, self.limit, self.alpha)
+            rows = torch._grouped_mm(act, self.down.transpose(1, 2), offs=ends, out_dtype=rt.dtype)
+        elif self.n_experts:
             act = ctx.buffer("moe.act", (n * top, self.intermediate), rt.dtype)
             ops.moe_rows_gemm(x, row_token, offsets, self.n_experts, n * top, self.gate_up, act, self.glu, self.limit, self.alpha)
             ops.moe_rows_gemm(act, None, offsets, self.n_experts, n * top, self.down, rows)

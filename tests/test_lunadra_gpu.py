@@ -295,6 +295,15 @@ ALONE = {
     "delta": {"type": "parallel", "mlp": None,
               "mixer": {"left": _left(1, 1, 8, 8, 0.5, 8, 0), "left_scale": 0.0, "right_scale": 1.0,
                         "right": {"heads": 6, "kv_heads": 2, "dim": 20, "vdim": 12, "conv": 4}}},
+    # key sizes beyond 64 (a state column in 128 registers) and beyond 128 (the state in shared memory)
+    "mlstm wide": {"type": "mlstm", "mixer": {"heads": 2, "dim": 96, "vdim": 136, "gate_cap": 9.0}, "mlp": None},
+    "mlstm widest": {"type": "mlstm", "mixer": {"heads": 1, "dim": 144, "vdim": 40, "gate_cap": 9.0}, "mlp": None},
+    "delta wide": {"type": "parallel", "mlp": None,
+                   "mixer": {"left": _left(1, 1, 8, 8, 0.5, 8, 0), "left_scale": 0.0, "right_scale": 1.0,
+                             "right": {"heads": 2, "kv_heads": 1, "dim": 80, "vdim": 96, "conv": 2}}},
+    "delta widest": {"type": "parallel", "mlp": None,
+                     "mixer": {"left": _left(1, 1, 8, 8, 0.5, 8, 0), "left_scale": 0.0, "right_scale": 1.0,
+                               "right": {"heads": 2, "kv_heads": 2, "dim": 136, "vdim": 24, "conv": 3}}},
     "dense": {"type": "mlstm", "mixer": {"heads": 1, "dim": 8, "vdim": 8, "gate_cap": 5.0}, "mlp": {"kind": "dense", "ff": 100}},
     "experts": {"type": "mlstm", "mixer": {"heads": 1, "dim": 8, "vdim": 8, "gate_cap": 5.0}, "mlp": _moe(7, 2, 2, 36, 1.0, shared=(20, 0.5))},
     "identity experts only": {"type": "mlstm", "mixer": {"heads": 1, "dim": 8, "vdim": 8, "gate_cap": 5.0}, "mlp": _moe(0, 3, 2, 8, 1.0)},
