@@ -157,7 +157,7 @@ long long pe_delta_rule_scratch_floats(int n_seqs, int heads, int d, int dv, int
 
 // moe.cu
 int pe_moe_route(const float* logits, const float* correction, int n_tokens, int n_all, int top, int* chosen,
-    float* weight, cudaStream_t stream);
+    float* weight, int* dense_rows, int n_real, cudaStream_t stream);
 int pe_moe_group(const int* chosen, int n_tokens, int top, int n_real, int* offsets, int* row_token, int* pair_row,
     cudaStream_t stream);
 int pe_moe_rows_gemm(int dtype, int out_dtype, const void* x, long long x_ld, const int* row_map, const int* offsets,

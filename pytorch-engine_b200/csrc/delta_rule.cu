@@ -8,8 +8,8 @@
 //   step         S <- diag(g) S ;  u = beta (v - S^T k) ;  S <- S + k u^T ;  o = S^T q            beta = sigmoid(b)
 //   out          = o / rms(o) * w * sigmoid(gate)                           per head, eps inside the root, w of size dv
 //
-// A block owns one head's S [d, dv] of one sequence in shared memory and walks the sequence's tokens of this step
-// in order; thread j owns column j.  State, decay, beta, the unit vectors and the head norm are float32 whatever
+// A block owns one head's S [d, dv] of one sequence (in registers or in shared memory) and walks the sequence's tokens
+// of this step in order; thread j owns column j.  State, decay, beta, the unit vectors and the head norm are float32 whatever
 // the run dtype.
 #include "api.h"
 #include "common.cuh"
@@ -44,6 +44,74 @@ __global__ void short_conv_kernel(const T* x, long long ld, int col0, const floa
       acc = fmaf(w[(size_t)c * taps + j], v, acc);
     }
     out[(size_t)t * channels + c] = from_f32<T>(acc / (1.f + expf(-acc)));
+  }
+}
+
+// The same for bfloat16 rows whose channels are a multiple of 8 and start on 16-byte boundaries: a thread takes eight
+// channels of a strip of eight tokens with its 8 x TAPS weights in registers (loaded once per strip: a weight load of
+// a warp touches 32 cache lines), 16-byte loads and stores.  A step of few tokens takes strips of one.
+
+template <int TAPS>
+__global__ void short_conv_vec8_kernel(const __nv_bfloat16* x, long long ld, int col0, const float* __restrict__ w,
+                                       const float* tail, const int* token_seq, const int* seq_slot, const int* seq_qstart,
+                                       __nv_bfloat16* __restrict__ out, int n_tokens, int channels, int n_slots, int* status,
+                                       int kConvStrip) {
+  const int per_row = channels / 8;
+  const int strips = (n_tokens + kConvStrip - 1) / kConvStrip;
+  const size_t total = (size_t)strips * per_row;
+  const size_t idx0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  float wr[8][TAPS];
+  int c_have = -1;
+  pdl_wait_block();
+  pdl_launch_dependents();
+  for (size_t idx = idx0; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int strip = (int)(idx / per_row), c = (int)(idx - (size_t)strip * per_row) * 8;
+    if (c != c_have) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wr[e][j] = w[(size_t)(c + e) * TAPS + j];
+      c_have = c;
+    }
+    const int t_end = min(n_tokens, (strip + 1) * kConvStrip);
+    for (int t = strip * kConvStrip; t < t_end; ++t) {
+      const int b = token_seq[t];
+      const int first = seq_qstart[b];
+      const int slot = seq_slot[b];
+      if (slot < 0 || slot >= n_slots) {
+        if (c == 0) report(status, kStatusSlotOutOfRange, t, slot, n_slots);
+        continue;
+      }
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) {
+        const int src = t - (TAPS - 1) + j;
+        float v[8];
+        if (src >= first) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)src * ld + col0 + c);
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h2[e]);
+            v[2 * e] = f.x; v[2 * e + 1] = f.y;
+          }
+        } else {
+          const float* tp = tail + ((size_t)slot * (TAPS - 1) + (TAPS - 1) - (first - src)) * channels + c;
+          const float4 a0 = *reinterpret_cast<const float4*>(tp), a1 = *reinterpret_cast<const float4*>(tp + 4);
+          v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w; v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(wr[e][j], v[e], acc[e]);
+      }
+      uint4 o;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        o2[e] = __floats2bfloat162_rn(acc[2 * e] / (1.f + expf(-acc[2 * e])), acc[2 * e + 1] / (1.f + expf(-acc[2 * e + 1])));
+      *reinterpret_cast<uint4*>(out + (size_t)t * channels + c) = o;
+    }
   }
 }
 
@@ -99,22 +167,41 @@ __host__ __device__ inline size_t delta_unit(int d, int dv) { return (size_t)d *
 // MODE 3: chunk blockIdx.z from its true start (as the chain kernel left it): writes outputs; the sequence's last chunk
 //         writes the state back.
 // DREG > 0: d <= DREG and thread j keeps its column in registers; DREG == 0: the matrix lives in shared memory.
-template <typename T, int MODE, int DREG>
-__global__ void __launch_bounds__(DREG == 0 ? 1024 : (DREG == 32 ? 512 : 256)) delta_rule_kernel(DeltaArgs a) {
-  extern __shared__ float sm[];
+//
+// Tokens are taken `batch` at a time: their q, k, v and gate rows are staged in shared memory with all loads in flight
+// at once, the decays, the vectors' lengths and beta are computed side by side; the walk over the batch's tokens then
+// reads shared memory only, and where no output is written (MODE 1) it needs no barrier at all.
+constexpr int kDeltaBatch = 32;
+
+template <typename T>
+__host__ __device__ inline size_t delta_smem_bytes(int d, int dv, int dreg, int batch) {
+  const size_t dpad = dreg > 0 ? dreg : d;
+  const size_t widest = dv > d ? dv : d;
+  return ((dreg > 0 ? 0 : (size_t)d * widest) + 3 * (size_t)batch * dpad) * sizeof(float) + 2 * (size_t)batch * dv * sizeof(T);
+}
+
+// SPLIT == 2: two threads share a column, each with 64 of its rows in registers; they are lanes l and l ^ 16 of one warp
+// and add their partial sums with one shuffle.  Half the registers a thread, so more warps an SM holds: the walk waits
+// on shared-memory and arithmetic latencies, which more warps hide.
+template <typename T, int MODE, int DREG, int SPLIT>
+__global__ void __launch_bounds__(DREG == 0 ? 1024 : 512) delta_rule_kernel(DeltaArgs a, int batch) {
+  extern __shared__ __align__(16) float sm[];
   __shared__ float red[32];
+  __shared__ float s_kn[kDeltaBatch], s_qn[kDeltaBatch], s_beta[kDeltaBatch];
   const int d = a.d, head = blockIdx.x, b = blockIdx.y;
   const int c = MODE == 1 ? blockIdx.z % a.max_chunks : blockIdx.z;
   const bool transition = MODE == 1 && (int)blockIdx.z >= a.max_chunks;
   const int dv = a.dv;
   const int cols = transition ? d : dv;            // columns of the matrix this block carries
   const int kvh = head / (a.heads / a.kv_heads);
-  constexpr int DP = DREG > 0 ? DREG : 1;
-  const int dpad = DREG > 0 ? DREG : d;
+  constexpr int DP = DREG > 0 ? DREG : 1;          // rows of a column that a thread keeps
+  const int dpad = DREG > 0 ? DREG * SPLIT : d;
   float* S = sm;                                   // [d][cols] (DREG == 0 only)
-  float* qs = S + (DREG > 0 ? 0 : (size_t)d * (dv > d ? dv : d));
-  float* ks = qs + dpad;
-  float* gs = ks + dpad;
+  float* qb = S + (DREG > 0 ? 0 : (size_t)d * (dv > d ? dv : d));   // [batch][dpad]
+  float* kb = qb + (size_t)batch * dpad;           // [batch][dpad]
+  float* db = kb + (size_t)batch * dpad;           // [batch][dpad]: the decays
+  T* vb = reinterpret_cast<T*>(db + (size_t)batch * dpad);   // [batch][dv]
+  T* gb = vb + (size_t)batch * dv;                 // [batch][dv]: the output gates before their sigmoid
   pdl_wait_block();
   pdl_launch_dependents();
   const int slot = a.seq_slot[b];
@@ -134,100 +221,167 @@ __global__ void __launch_bounds__(DREG == 0 ? 1024 : (DREG == 32 ? 512 : 256)) d
   float* cs = MODE != 0 ? a.scratch + (((size_t)b * a.max_chunks + c) * a.heads + head) * unit : nullptr;
   float* gS = a.S + ((size_t)slot * a.heads + head) * d * dv;
   const float* src = MODE == 0 ? gS : cs;
-  const int j = threadIdx.x;
+  // the thread's column and, with two threads a column, the first of its rows
+  const int j = SPLIT == 2 ? (threadIdx.x >> 5) * 16 + (threadIdx.x & 15) : threadIdx.x;
+  const int i0 = SPLIT == 2 ? ((threadIdx.x >> 4) & 1) * DP : 0;
   float Sr[DP];
   if (MODE == 1) {
     if (DREG > 0) {
 #pragma unroll
-      for (int i = 0; i < DP; ++i) Sr[i] = (transition && i == j) ? 1.f : 0.f;
+      for (int i = 0; i < DP; ++i) Sr[i] = (transition && i0 + i == j) ? 1.f : 0.f;
     } else {
       for (int i = threadIdx.x; i < d * cols; i += blockDim.x) S[i] = (transition && i / cols == i % cols) ? 1.f : 0.f;
     }
   } else {
     if (DREG > 0) {
 #pragma unroll
-      for (int i = 0; i < DP; ++i) Sr[i] = (i < d && j < dv) ? src[(size_t)i * dv + j] : 0.f;
+      for (int i = 0; i < DP; ++i) Sr[i] = (i0 + i < d && j < dv) ? src[(size_t)(i0 + i) * dv + j] : 0.f;
     } else {
       for (int i = threadIdx.x; i < d * dv; i += blockDim.x) S[i] = src[i];
     }
   }
-  for (int i = d + threadIdx.x; i < dpad; i += blockDim.x) { qs[i] = 0.f; ks[i] = 0.f; gs[i] = 0.f; }
+  if (dpad > d)
+    for (int e = threadIdx.x; e < batch * (dpad - d); e += blockDim.x) {
+      const int tt = e / (dpad - d), i = d + e % (dpad - d);
+      qb[(size_t)tt * dpad + i] = 0.f;
+      kb[(size_t)tt * dpad + i] = 0.f;
+      db[(size_t)tt * dpad + i] = 0.f;
+    }
   const int channels = 2 * a.kv_heads * d + a.heads * dv;
   const int k_col = a.kv_heads * d, v_col = 2 * a.kv_heads * d;
   const T* x = (const T*)a.qkv;
   const float rate = expf(a.A_log[head]);
   const float nw = (MODE != 1 && j < dv) ? a.norm_w[j] : 0.f;
-  __syncthreads();
-  for (int t = t0; t < t1; ++t) {
-    float q2 = 0.f, k2 = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-      const float kk = to_f32<T>(x[(size_t)t * channels + k_col + kvh * d + i]);
-      ks[i] = kk;
-      k2 += kk * kk;
-      if (MODE != 1) {
-        const float qq = to_f32<T>(x[(size_t)t * channels + kvh * d + i]);
-        qs[i] = qq;
-        q2 += qq * qq;
-      }
-      const float z = a.a[(size_t)t * a.heads * d + head * d + i] + a.dt_bias[head * d + i];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  for (int tb = t0; tb < t1; tb += batch) {
+    const int nb = min(batch, t1 - tb);
+    __syncthreads();                               // the batch before this one has been read
+    for (int e = threadIdx.x; e < nb * d; e += blockDim.x) {
+      const int tt = e / d, i = e - tt * d;
+      const size_t row = (size_t)(tb + tt) * channels;
+      kb[(size_t)tt * dpad + i] = to_f32<T>(x[row + k_col + kvh * d + i]);
+      if (MODE != 1) qb[(size_t)tt * dpad + i] = to_f32<T>(x[row + kvh * d + i]);
+      const float z = a.a[(size_t)(tb + tt) * a.heads * d + head * d + i] + a.dt_bias[head * d + i];
       const float softplus = z > 20.f ? z : log1pf(expf(z));
-      gs[i] = expf(-rate * softplus);
+      db[(size_t)tt * dpad + i] = expf(-rate * softplus);
     }
-    k2 = block_sum(k2, red);
-    if (MODE != 1) q2 = block_sum(q2, red);
-    const float qn = rsqrtf(q2 + 1e-6f) * a.q_scale, kn = rsqrtf(k2 + 1e-6f);
-    const float beta = 1.f / (1.f + expf(-a.b[(size_t)t * a.heads + head]));
-    float o = 0.f;
-    if (j < cols) {
-      float acc = 0.f;
-      const float vj = transition ? 0.f : to_f32<T>(x[(size_t)t * channels + v_col + head * dv + j]);
-      if (DREG > 0) {
-#pragma unroll
-        for (int i = 0; i < DP; i += 4) {
-          const float4 g4 = *reinterpret_cast<const float4*>(gs + i);
-          const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            Sr[i + e] *= (&g4.x)[e];
-            acc = fmaf(Sr[i + e], (&k4.x)[e], acc);
-          }
-        }
-        const float uk = beta * (vj - acc * kn) * kn;
-#pragma unroll
-        for (int i = 0; i < DP; i += 4) {
-          const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) Sr[i + e] = fmaf((&k4.x)[e], uk, Sr[i + e]);
-          if (MODE != 1) {
-            const float4 q4 = *reinterpret_cast<const float4*>(qs + i);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) o = fmaf(Sr[i + e], (&q4.x)[e], o);
-          }
-        }
-      } else {
-        for (int i = 0; i < d; ++i) {
-          const float s = gs[i] * S[(size_t)i * cols + j];
-          S[(size_t)i * cols + j] = s;
-          acc = fmaf(s, ks[i], acc);
-        }
-        const float uk = beta * (vj - acc * kn) * kn;
-        for (int i = 0; i < d; ++i) {
-          const float s = fmaf(ks[i], uk, S[(size_t)i * cols + j]);
-          S[(size_t)i * cols + j] = s;
-          if (MODE != 1) o = fmaf(s, qs[i], o);
+    if (!transition)
+      for (int e = threadIdx.x; e < nb * dv; e += blockDim.x) {
+        const int tt = e / dv, jj = e - tt * dv;
+        vb[e] = x[(size_t)(tb + tt) * channels + v_col + head * dv + jj];
+        if (MODE != 1) gb[e] = ((const T*)a.gate)[(size_t)(tb + tt) * a.gate_ld + head * dv + jj];
+      }
+    if (threadIdx.x < nb) s_beta[threadIdx.x] = 1.f / (1.f + expf(-a.b[(size_t)(tb + threadIdx.x) * a.heads + head]));
+    __syncthreads();
+    for (int tt = warp; tt < nb; tt += n_warps) {  // a warp per token: the lengths of k and q
+      float k2 = 0.f, q2 = 0.f;
+      for (int i = lane; i < d; i += 32) {
+        const float kk = kb[(size_t)tt * dpad + i];
+        k2 = fmaf(kk, kk, k2);
+        if (MODE != 1) {
+          const float qq = qb[(size_t)tt * dpad + i];
+          q2 = fmaf(qq, qq, q2);
         }
       }
-      o *= qn;
+      k2 = warp_sum(k2);
+      q2 = warp_sum(q2);
+      if (lane == 0) {
+        s_kn[tt] = rsqrtf(k2 + 1e-6f);
+        s_qn[tt] = rsqrtf(q2 + 1e-6f) * a.q_scale;
+      }
     }
-    if (MODE == 1) {
-      __syncthreads();                             // this token's k and g have been read before the next are written
-      continue;
-    }
-    const float ss = block_sum(o * o, red);
-    if (j < dv) {
-      const float gate = to_f32<T>(((const T*)a.gate)[(size_t)t * a.gate_ld + head * dv + j]);
-      const float y = o * rsqrtf(ss / (float)dv + a.eps) * nw / (1.f + expf(-gate));
-      ((T*)a.out)[(size_t)t * a.heads * dv + head * dv + j] = from_f32<T>(y);
+    __syncthreads();
+    for (int tt = 0; tt < nb; ++tt) {
+      const float kn = s_kn[tt], qn = s_qn[tt], beta = s_beta[tt];
+      const float* ks = kb + (size_t)tt * dpad;
+      const float* qs = qb + (size_t)tt * dpad;
+      const float* gs = db + (size_t)tt * dpad;
+      float o = 0.f;
+      if (DREG > 0 && SPLIT == 2) {
+        // whole warps walk together (the two halves of a column meet in a shuffle); a column beyond the matrix
+        // carries zeros and is never stored
+        float acc = 0.f;
+        const float vj = (transition || j >= dv) ? 0.f : to_f32<T>(vb[(size_t)tt * dv + j]);
+#pragma unroll
+        for (int i = 0; i < DP; i += 4) {
+          const float4 g4 = *reinterpret_cast<const float4*>(gs + i0 + i);
+          const float4 k4 = *reinterpret_cast<const float4*>(ks + i0 + i);
+          Sr[i] *= g4.x; Sr[i + 1] *= g4.y; Sr[i + 2] *= g4.z; Sr[i + 3] *= g4.w;
+          acc = fmaf(Sr[i], k4.x, acc);
+          acc = fmaf(Sr[i + 1], k4.y, acc);
+          acc = fmaf(Sr[i + 2], k4.z, acc);
+          acc = fmaf(Sr[i + 3], k4.w, acc);
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+        const float uk = beta * (vj - acc * kn) * kn;
+#pragma unroll
+        for (int i = 0; i < DP; i += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(ks + i0 + i);
+          Sr[i] = fmaf(k4.x, uk, Sr[i]);
+          Sr[i + 1] = fmaf(k4.y, uk, Sr[i + 1]);
+          Sr[i + 2] = fmaf(k4.z, uk, Sr[i + 2]);
+          Sr[i + 3] = fmaf(k4.w, uk, Sr[i + 3]);
+          if (MODE != 1) {
+            const float4 q4 = *reinterpret_cast<const float4*>(qs + i0 + i);
+            o = fmaf(Sr[i], q4.x, o);
+            o = fmaf(Sr[i + 1], q4.y, o);
+            o = fmaf(Sr[i + 2], q4.z, o);
+            o = fmaf(Sr[i + 3], q4.w, o);
+          }
+        }
+        if (MODE != 1) o = (o + __shfl_xor_sync(0xffffffffu, o, 16)) * qn;
+      } else if (j < cols) {
+        float acc = 0.f;
+        const float vj = transition ? 0.f : to_f32<T>(vb[(size_t)tt * dv + j]);
+        if (DREG > 0) {
+#pragma unroll
+          for (int i = 0; i < DP; i += 4) {
+            const float4 g4 = *reinterpret_cast<const float4*>(gs + i);
+            const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
+            Sr[i] *= g4.x; Sr[i + 1] *= g4.y; Sr[i + 2] *= g4.z; Sr[i + 3] *= g4.w;
+            acc = fmaf(Sr[i], k4.x, acc);
+            acc = fmaf(Sr[i + 1], k4.y, acc);
+            acc = fmaf(Sr[i + 2], k4.z, acc);
+            acc = fmaf(Sr[i + 3], k4.w, acc);
+          }
+          const float uk = beta * (vj - acc * kn) * kn;
+#pragma unroll
+          for (int i = 0; i < DP; i += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
+            Sr[i] = fmaf(k4.x, uk, Sr[i]);
+            Sr[i + 1] = fmaf(k4.y, uk, Sr[i + 1]);
+            Sr[i + 2] = fmaf(k4.z, uk, Sr[i + 2]);
+            Sr[i + 3] = fmaf(k4.w, uk, Sr[i + 3]);
+            if (MODE != 1) {
+              const float4 q4 = *reinterpret_cast<const float4*>(qs + i);
+              o = fmaf(Sr[i], q4.x, o);
+              o = fmaf(Sr[i + 1], q4.y, o);
+              o = fmaf(Sr[i + 2], q4.z, o);
+              o = fmaf(Sr[i + 3], q4.w, o);
+            }
+          }
+        } else {
+          for (int i = 0; i < d; ++i) {
+            const float s = gs[i] * S[(size_t)i * cols + j];
+            S[(size_t)i * cols + j] = s;
+            acc = fmaf(s, ks[i], acc);
+          }
+          const float uk = beta * (vj - acc * kn) * kn;
+          for (int i = 0; i < d; ++i) {
+            const float s = fmaf(ks[i], uk, S[(size_t)i * cols + j]);
+            S[(size_t)i * cols + j] = s;
+            if (MODE != 1) o = fmaf(s, qs[i], o);
+          }
+        }
+        o *= qn;
+      }
+      if (MODE == 1) continue;                     // a column is its own thread's, the staged rows are only read
+      const float ss = block_sum((i0 == 0 && j < dv) ? o * o : 0.f, red);
+      if (j < dv && i0 == 0) {
+        const float gate = to_f32<T>(gb[(size_t)tt * dv + j]);
+        const float y = o * rsqrtf(ss / (float)dv + a.eps) * nw / (1.f + expf(-gate));
+        ((T*)a.out)[(size_t)(tb + tt) * a.heads * dv + head * dv + j] = from_f32<T>(y);
+      }
     }
   }
   __syncthreads();
@@ -237,7 +391,7 @@ __global__ void __launch_bounds__(DREG == 0 ? 1024 : (DREG == 32 ? 512 : 256)) d
     if (j < cols) {
 #pragma unroll
       for (int i = 0; i < DP; ++i)
-        if (i < d) dst[(size_t)i * cols + j] = Sr[i];
+        if (i0 + i < d) dst[(size_t)(i0 + i) * cols + j] = Sr[i];
     }
   } else {
     for (int i = threadIdx.x; i < d * cols; i += blockDim.x) dst[i] = S[i];
@@ -287,19 +441,21 @@ __global__ void delta_chain_kernel(DeltaArgs a, int col_tile) {
   }
 }
 
-template <typename T, int DREG>
+template <typename T, int DREG, int SPLIT>
 static int delta_run(const DeltaArgs& a, cudaStream_t stream) {
   const int d = a.d, dv = a.dv;
-  const int dpad = DREG > 0 ? DREG : d;
   const int widest = dv > d ? dv : d;
-  const size_t smem = ((DREG > 0 ? 0 : (size_t)d * widest) + 3 * (size_t)dpad) * sizeof(float);
-  int threads = (widest + 31) / 32 * 32;
-  const int cap_threads = DREG == 0 ? 1024 : (DREG == 32 ? 512 : 256);
+  int batch = kDeltaBatch;                       // as many tokens staged at a time as shared memory takes
+  while (batch > 1 && delta_smem_bytes<T>(d, dv, DREG * SPLIT, batch) > 200 * 1024) batch /= 2;
+  const size_t smem = delta_smem_bytes<T>(d, dv, DREG * SPLIT, batch);
+  if (smem > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;
+  int threads = (SPLIT * widest + 31) / 32 * 32;
+  const int cap_threads = DREG == 0 ? 1024 : 512;
   if (threads > cap_threads) threads = cap_threads;
-  if (widest > threads) return PE_ERR_UNSUPPORTED_SIZE;
-  auto k0 = delta_rule_kernel<T, 0, DREG>;
-  auto k1 = delta_rule_kernel<T, 1, DREG>;
-  auto k3 = delta_rule_kernel<T, 3, DREG>;
+  if (SPLIT * widest > threads) return PE_ERR_UNSUPPORTED_SIZE;
+  auto k0 = delta_rule_kernel<T, 0, DREG, SPLIT>;
+  auto k1 = delta_rule_kernel<T, 1, DREG, SPLIT>;
+  auto k3 = delta_rule_kernel<T, 3, DREG, SPLIT>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -307,7 +463,7 @@ static int delta_run(const DeltaArgs& a, cudaStream_t stream) {
     if (e != cudaSuccess) return (int)e;
   }
   if (a.chunk > 0) {
-    launch(k1, dim3(a.heads, a.n_seqs, 2 * a.max_chunks), dim3(threads), smem, stream, a);
+    launch(k1, dim3(a.heads, a.n_seqs, 2 * a.max_chunks), dim3(threads), smem, stream, a, batch);
     int col_tile = 1024 / d;
     if (col_tile > 8) col_tile = 8;
     if (col_tile < 1) return PE_ERR_UNSUPPORTED_SIZE;
@@ -319,9 +475,9 @@ static int delta_run(const DeltaArgs& a, cudaStream_t stream) {
     }
     launch(delta_chain_kernel, dim3(a.heads, a.n_seqs, (dv + col_tile - 1) / col_tile), dim3(col_tile * d), chain_smem, stream, a,
            col_tile);
-    launch(k3, dim3(a.heads, a.n_seqs, a.max_chunks), dim3(threads), smem, stream, a);
+    launch(k3, dim3(a.heads, a.n_seqs, a.max_chunks), dim3(threads), smem, stream, a, batch);
   } else {
-    launch(k0, dim3(a.heads, a.n_seqs, 1), dim3(threads), smem, stream, a);
+    launch(k0, dim3(a.heads, a.n_seqs, 1), dim3(threads), smem, stream, a, batch);
   }
   return PE_OK;
 }
@@ -335,7 +491,17 @@ extern "C" int pe_short_conv_silu(int dtype, const void* x, long long ld, int co
   if (channels <= 0 || taps <= 0 || taps > 64 || col0 < 0 || col0 + channels > ld) return PE_ERR_BAD_ARGUMENT;
   const int threads = channels >= 1024 ? 256 : 128;
   if (dtype != PE_F32 && dtype != PE_BF16) return PE_ERR_UNSUPPORTED_DTYPE;
-  if (dtype == PE_F32)
+  const bool vec8 = dtype == PE_BF16 && taps >= 2 && taps <= 4 && channels % 8 == 0 && ld % 8 == 0 && col0 % 8 == 0 &&
+                    (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)tail % 16 == 0;
+  if (vec8) {
+    const int strip = n_tokens >= 512 ? 8 : 1;
+    const size_t total = (size_t)((n_tokens + strip - 1) / strip) * (channels / 8);
+    size_t blocks = (total + 127) / 128;
+    if (blocks > (size_t)pe::kSMs * 32) blocks = (size_t)pe::kSMs * 32;
+    auto kernel = taps == 2 ? pe::short_conv_vec8_kernel<2> : (taps == 3 ? pe::short_conv_vec8_kernel<3> : pe::short_conv_vec8_kernel<4>);
+    pe::launch(kernel, (int)blocks, 128, 0, stream, (const __nv_bfloat16*)x, ld, col0, w, (const float*)tail, token_seq, seq_slot,
+               seq_qstart, (__nv_bfloat16*)out, n_tokens, channels, n_slots, status, strip);
+  } else if (dtype == PE_F32)
     pe::launch(pe::short_conv_kernel<float>, n_tokens, threads, 0, stream, (const float*)x, ld, col0, w, taps, (const float*)tail,
                token_seq, seq_slot, seq_qstart, (float*)out, n_tokens, channels, n_slots, status);
   else
@@ -378,13 +544,15 @@ extern "C" int pe_delta_rule_recurrence(int dtype, const void* qkv, const float*
     args.chunk = chunk; args.max_chunks = max_chunks; args.scratch = scratch;
   }
   const int widest = dv > d ? dv : d;
-  const int reg = (d <= 32 && widest <= 512) ? 32 : (d <= 64 && widest <= 256 ? 64 : (d <= 128 && widest <= 256 ? 128 : 0));
-  if (reg == 0 && ((size_t)d * widest + 3 * (size_t)d) * sizeof(float) > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;
+  // 128: two threads a column with 64 rows each (the columns then fill whole half-warps)
+  const int reg = (d <= 32 && widest <= 512) ? 32
+                  : (d <= 64 && widest <= 512 ? 64 : (d <= 128 && widest <= 256 && dv % 16 == 0 && d % 16 == 0 ? 128 : 0));
+  if (reg == 0 && ((size_t)d * widest + 3 * (size_t)d + 2 * (size_t)dv) * sizeof(float) > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;
   int rc;
 #define PE_DELTA(T)                                                       \
-  (reg == 32 ? pe::delta_run<T, 32>(args, stream)                         \
-   : reg == 64 ? pe::delta_run<T, 64>(args, stream)                       \
-   : reg == 128 ? pe::delta_run<T, 128>(args, stream) : pe::delta_run<T, 0>(args, stream))
+  (reg == 32 ? pe::delta_run<T, 32, 1>(args, stream)                      \
+   : reg == 64 ? pe::delta_run<T, 64, 1>(args, stream)                    \
+   : reg == 128 ? pe::delta_run<T, 64, 2>(args, stream) : pe::delta_run<T, 0, 1>(args, stream))
   rc = dtype == PE_F32 ? PE_DELTA(float) : PE_DELTA(__nv_bfloat16);
 #undef PE_DELTA
   if (rc != PE_OK) return rc;

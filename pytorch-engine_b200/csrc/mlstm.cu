@@ -7,8 +7,8 @@
 //   read      o    = S'^T q / (max(|n' . q|, e^(-m')) + 1e-6)     q already carries its factor d^(-1/2)
 //   out       = o / rms(o) * w * sigmoid(g)                 per head, eps inside the root
 //
-// A block owns one head's S [d, dv], n [d] and m of one sequence in shared memory and walks the sequence's tokens
-// of this step in order; thread j owns column j of S.  Gates, state, the read's denominator and the head norm are
+// A block owns one head's S [d, dv], n [d] and m of one sequence (S in registers or in shared memory) and walks the
+// sequence's tokens of this step in order; thread j owns column j of S.  Gates, state, the read's denominator and the head norm are
 // float32 whatever the run dtype; q, k, v, g come from matrix products in the run dtype, the two gate
 // pre-activations from a product that writes float32.
 #include "api.h"
@@ -51,17 +51,36 @@ __host__ __device__ inline size_t mlstm_unit(int d, int dv) { return (size_t)d *
 // MODE 3: chunk blockIdx.z from its true start (as the chain kernel left it): writes outputs; the sequence's last chunk
 //         writes the state back.
 // DREG > 0: d <= DREG and thread j keeps its column of S in registers; DREG == 0: S lives in shared memory.
-template <typename T, int MODE, int DREG>
-__global__ void __launch_bounds__(DREG == 128 ? 256 : (DREG == 64 ? 512 : 1024)) mlstm_kernel(MlstmArgs a) {
-  extern __shared__ float sm[];
+//
+// Tokens are taken `batch` at a time: their k, q, v, g rows are staged in shared memory with all loads in flight at
+// once, their gates are computed side by side, and one thread runs the chain of maxima over the batch; the walk over
+// the batch's tokens then reads shared memory only (a walk that loads each token's rows when it gets there spends most
+// of its time waiting for them).
+constexpr int kMlstmBatch = 32;
+
+template <typename T>
+__host__ __device__ inline size_t mlstm_smem_bytes(int d, int dv, int dreg, int batch) {
+  const size_t dpad = dreg > 0 ? dreg : d;       // dreg: the padded key size of a register variant
+  return ((dreg > 0 ? 0 : (size_t)d * dv) + dpad + 2 * (size_t)batch * dpad) * sizeof(float) + 2 * (size_t)batch * dv * sizeof(T);
+}
+
+// SPLIT == 2 (with DREG == 128): two threads share a column, each with 64 of its rows in registers; they are lanes l and
+// l ^ 16 of one warp and add their partial sums with one shuffle.  Half the registers a thread, so four times the
+// warps an SM holds: the walk waits on shared-memory and arithmetic latencies, which more warps hide.
+template <typename T, int MODE, int DREG, int SPLIT>
+__global__ void __launch_bounds__(DREG == 64 ? 512 : 1024) mlstm_kernel(MlstmArgs a, int batch) {
+  extern __shared__ __align__(16) float sm[];
   __shared__ float red[32];
+  __shared__ float s_keep[kMlstmBatch], s_take[kMlstmBatch], s_em[kMlstmBatch];
   const int d = a.d, dv = a.dv, head = blockIdx.x, b = blockIdx.y, c = blockIdx.z;
-  constexpr int DP = DREG > 0 ? DREG : 1;
-  const int dpad = DREG > 0 ? DREG : d;            // vectors are padded with zeros up to the register tile
+  constexpr int DP = DREG > 0 ? DREG : 1;          // rows of a column that a thread keeps
+  const int dpad = DREG > 0 ? DREG * SPLIT : d;    // vectors are padded with zeros up to the register tile
   float* S = sm;                                   // [d][dv] (DREG == 0 only)
   float* nvec = S + (DREG > 0 ? 0 : (size_t)d * dv);
-  float* qs = nvec + dpad;
-  float* ks = qs + dpad;
+  float* kb = nvec + dpad;                         // [batch][dpad]
+  float* qb = kb + (size_t)batch * dpad;           // [batch][dpad]
+  T* vb = reinterpret_cast<T*>(qb + (size_t)batch * dpad);   // [batch][dv]
+  T* gb = vb + (size_t)batch * dv;                 // [batch][dv]
   pdl_wait_block();
   pdl_launch_dependents();
   const int slot = a.seq_slot[b];
@@ -83,9 +102,11 @@ __global__ void __launch_bounds__(DREG == 128 ? 256 : (DREG == 64 ? 512 : 1024))
   float* gn = a.n + ((size_t)slot * a.heads + head) * d;
   const float* src_S = MODE == 0 ? gS : cs;
   const float* src_n = MODE == 0 ? gn : cs + (size_t)d * dv;
-  const int j = threadIdx.x;
+  // the thread's column and, with two threads a column, the first of its rows
+  const int j = SPLIT == 2 ? (threadIdx.x >> 5) * 16 + (threadIdx.x & 15) : threadIdx.x;
+  const int i0 = SPLIT == 2 ? ((threadIdx.x >> 4) & 1) * DP : 0;
   float Sr[DP];
-  float m;
+  float m;                                         // followed by thread 0
   if (MODE == 1) {
     if (DREG > 0) {
 #pragma unroll
@@ -98,73 +119,108 @@ __global__ void __launch_bounds__(DREG == 128 ? 256 : (DREG == 64 ? 512 : 1024))
   } else {
     if (DREG > 0) {
 #pragma unroll
-      for (int i = 0; i < DP; ++i) Sr[i] = (i < d && j < dv) ? src_S[(size_t)i * dv + j] : 0.f;
+      for (int i = 0; i < DP; ++i) Sr[i] = (i0 + i < d && j < dv) ? src_S[(size_t)(i0 + i) * dv + j] : 0.f;
     } else {
       for (int i = threadIdx.x; i < d * dv; i += blockDim.x) S[i] = src_S[i];
     }
     for (int i = threadIdx.x; i < dpad; i += blockDim.x) nvec[i] = i < d ? src_n[i] : 0.f;
     m = MODE == 0 ? a.m[(size_t)slot * a.heads + head] : cs[unit - 1];
   }
-  for (int i = d + threadIdx.x; i < dpad; i += blockDim.x) qs[i] = ks[i] = 0.f;
+  if (dpad > d)
+    for (int e = threadIdx.x; e < batch * (dpad - d); e += blockDim.x) {
+      const int tt = e / (dpad - d), i = d + e % (dpad - d);
+      kb[(size_t)tt * dpad + i] = 0.f;
+      qb[(size_t)tt * dpad + i] = 0.f;
+    }
   float fsum = 0.f;
   const float bi = a.gate_bias[head], bf = a.gate_bias[a.heads + head];
+  const float nw = (MODE != 1 && j < dv) ? a.norm_w[head * dv + j] : 0.f;
   const T* q = (const T*)a.q; const T* k = (const T*)a.k; const T* v = (const T*)a.v; const T* g = (const T*)a.g;
-  __syncthreads();
-  for (int t = t0; t < t1; ++t) {
-    const float gi = a.cap * tanhf((a.gates[(size_t)t * 2 * a.heads + head] + bi) / a.cap);
-    const float gf = log_sigmoid(a.cap * tanhf((a.gates[(size_t)t * 2 * a.heads + a.heads + head] + bf) / a.cap));
-    const float m_new = fmaxf(gf + m, gi);
-    const float keep = expf(gf + m - m_new), take = expf(gi - m_new);
-    m = m_new;
-    fsum += gf;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-      const float kk = to_f32<T>(k[(size_t)t * a.ld + head * d + i]);
-      if (MODE != 1) qs[i] = to_f32<T>(q[(size_t)t * a.ld + head * d + i]) * a.q_scale;
-      ks[i] = kk;
-      nvec[i] = keep * nvec[i] + take * kk;
+  for (int tb = t0; tb < t1; tb += batch) {
+    const int nb = min(batch, t1 - tb);
+    __syncthreads();                               // the batch before this one has been read
+    for (int e = threadIdx.x; e < nb * d; e += blockDim.x) {
+      const int tt = e / d, i = e - tt * d;
+      kb[(size_t)tt * dpad + i] = to_f32<T>(k[(size_t)(tb + tt) * a.ld + head * d + i]);
+      if (MODE != 1) qb[(size_t)tt * dpad + i] = to_f32<T>(q[(size_t)(tb + tt) * a.ld + head * d + i]) * a.q_scale;
+    }
+    for (int e = threadIdx.x; e < nb * dv; e += blockDim.x) {
+      const int tt = e / dv, jj = e - tt * dv;
+      vb[e] = v[(size_t)(tb + tt) * a.ld + head * dv + jj];
+      if (MODE != 1) gb[e] = g[(size_t)(tb + tt) * a.ld + head * dv + jj];
+    }
+    if (threadIdx.x < nb) {
+      const int t = tb + threadIdx.x;
+      s_keep[threadIdx.x] = a.cap * tanhf((a.gates[(size_t)t * 2 * a.heads + head] + bi) / a.cap);
+      s_take[threadIdx.x] = log_sigmoid(a.cap * tanhf((a.gates[(size_t)t * 2 * a.heads + a.heads + head] + bf) / a.cap));
     }
     __syncthreads();
-    float o = 0.f;
-    if (j < dv) {
-      const float tv = take * to_f32<T>(v[(size_t)t * a.ld + head * dv + j]);
-      float acc = 0.f, nq = 0.f;
-      if (DREG > 0) {
+    if (threadIdx.x == 0) {
+      for (int tt = 0; tt < nb; ++tt) {
+        const float gi = s_keep[tt], gf = s_take[tt];
+        const float m_new = fmaxf(gf + m, gi);
+        s_keep[tt] = expf(gf + m - m_new);
+        s_take[tt] = expf(gi - m_new);
+        s_em[tt] = expf(-m_new);
+        m = m_new;
+        fsum += gf;
+      }
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nb; ++tt) {
+      const float keep = s_keep[tt], take = s_take[tt];
+      const float* ks = kb + (size_t)tt * dpad;
+      const float* qs = qb + (size_t)tt * dpad;
+      for (int i = threadIdx.x; i < d; i += blockDim.x) nvec[i] = keep * nvec[i] + take * ks[i];
+      if (MODE != 1) __syncthreads();              // every thread reads n below
+      float o = 0.f;
+      if (j < dv) {
+        const float tv = take * to_f32<T>(vb[(size_t)tt * dv + j]);
+        float acc = 0.f, nq = 0.f;
+        if (DREG > 0) {
 #pragma unroll
-        for (int i = 0; i < DP; i += 4) {
-          const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) Sr[i + e] = fmaf(keep, Sr[i + e], (&k4.x)[e] * tv);
-          if (MODE != 1) {
-            const float4 q4 = *reinterpret_cast<const float4*>(qs + i);
-            const float4 n4 = *reinterpret_cast<const float4*>(nvec + i);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              acc = fmaf(Sr[i + e], (&q4.x)[e], acc);
-              nq = fmaf((&n4.x)[e], (&q4.x)[e], nq);
+          for (int i = 0; i < DP; i += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(ks + i0 + i);
+            Sr[i] = fmaf(keep, Sr[i], k4.x * tv);
+            Sr[i + 1] = fmaf(keep, Sr[i + 1], k4.y * tv);
+            Sr[i + 2] = fmaf(keep, Sr[i + 2], k4.z * tv);
+            Sr[i + 3] = fmaf(keep, Sr[i + 3], k4.w * tv);
+            if (MODE != 1) {
+              const float4 q4 = *reinterpret_cast<const float4*>(qs + i0 + i);
+              const float4 n4 = *reinterpret_cast<const float4*>(nvec + i0 + i);
+              acc = fmaf(Sr[i], q4.x, acc);
+              acc = fmaf(Sr[i + 1], q4.y, acc);
+              acc = fmaf(Sr[i + 2], q4.z, acc);
+              acc = fmaf(Sr[i + 3], q4.w, acc);
+              nq = fmaf(n4.x, q4.x, nq);
+              nq = fmaf(n4.y, q4.y, nq);
+              nq = fmaf(n4.z, q4.z, nq);
+              nq = fmaf(n4.w, q4.w, nq);
+            }
+          }
+          if (SPLIT == 2 && MODE != 1) {           // the column's other half
+            acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+            nq += __shfl_xor_sync(0xffffffffu, nq, 16);
+          }
+        } else {
+          for (int i = 0; i < d; ++i) {
+            const float s = fmaf(keep, S[(size_t)i * dv + j], ks[i] * tv);
+            S[(size_t)i * dv + j] = s;
+            if (MODE != 1) {
+              acc = fmaf(s, qs[i], acc);
+              nq = fmaf(nvec[i], qs[i], nq);
             }
           }
         }
-      } else {
-        for (int i = 0; i < d; ++i) {
-          const float s = fmaf(keep, S[(size_t)i * dv + j], ks[i] * tv);
-          S[(size_t)i * dv + j] = s;
-          if (MODE != 1) {
-            acc = fmaf(s, qs[i], acc);
-            nq = fmaf(nvec[i], qs[i], nq);
-          }
-        }
+        o = acc / (fmaxf(fabsf(nq), s_em[tt]) + 1e-6f);
       }
-      o = acc / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
-    }
-    if (MODE == 1) {
-      __syncthreads();                           // this token's k has been read before the next one is written
-      continue;
-    }
-    const float ss = block_sum(o * o, red);   // its barriers also order this token's reads of q, k before the next writes
-    if (j < dv) {
-      const float gate = to_f32<T>(g[(size_t)t * a.ld + head * dv + j]);
-      const float y = o * rsqrtf(ss / (float)dv + a.eps) * a.norm_w[head * dv + j] / (1.f + expf(-gate));
-      ((T*)a.out)[(size_t)t * a.heads * dv + head * dv + j] = from_f32<T>(y);
+      if (MODE == 1) continue;                     // n[i] is its own thread's, the staged rows are only read
+      const float ss = block_sum(i0 == 0 ? o * o : 0.f, red);   // its barriers also put this token's reads of n before the next update
+      if (j < dv && i0 == 0) {
+        const float gate = to_f32<T>(gb[(size_t)tt * dv + j]);
+        const float y = o * rsqrtf(ss / (float)dv + a.eps) * nw / (1.f + expf(-gate));
+        ((T*)a.out)[(size_t)(tb + tt) * a.heads * dv + head * dv + j] = from_f32<T>(y);
+      }
     }
   }
   __syncthreads();
@@ -175,7 +231,7 @@ __global__ void __launch_bounds__(DREG == 128 ? 256 : (DREG == 64 ? 512 : 1024))
     if (j < dv) {
 #pragma unroll
       for (int i = 0; i < DP; ++i)
-        if (i < d) dst_S[(size_t)i * dv + j] = Sr[i];
+        if (i0 + i < d) dst_S[(size_t)(i0 + i) * dv + j] = Sr[i];
     }
   } else {
     for (int i = threadIdx.x; i < d * dv; i += blockDim.x) dst_S[i] = S[i];
@@ -223,19 +279,21 @@ __global__ void mlstm_chain_kernel(MlstmArgs a) {
   }
 }
 
-template <typename T, int DREG>
+template <typename T, int DREG, int SPLIT>
 static int mlstm_run(const MlstmArgs& a, int max_q, cudaStream_t stream) {
   const int d = a.d, dv = a.dv;
-  const int dpad = DREG > 0 ? DREG : d;
-  const size_t smem = ((DREG > 0 ? 0 : (size_t)d * dv) + 3 * (size_t)dpad) * sizeof(float);
+  int batch = kMlstmBatch;                       // as many tokens staged at a time as shared memory takes
+  while (batch > 1 && mlstm_smem_bytes<T>(d, dv, DREG * SPLIT, batch) > 200 * 1024) batch /= 2;
+  const size_t smem = mlstm_smem_bytes<T>(d, dv, DREG * SPLIT, batch);
+  if (smem > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;
   const int widest = dv > d ? dv : d;
-  int threads = (widest + 31) / 32 * 32;
-  const int cap_threads = DREG == 128 ? 256 : (DREG == 64 ? 512 : 1024);
+  int threads = (SPLIT * widest + 31) / 32 * 32;
+  const int cap_threads = DREG == 64 ? 512 : 1024;
   if (threads > cap_threads) threads = cap_threads;
-  if (DREG > 0 && dv > threads) return PE_ERR_UNSUPPORTED_SIZE;
-  auto k0 = mlstm_kernel<T, 0, DREG>;
-  auto k1 = mlstm_kernel<T, 1, DREG>;
-  auto k3 = mlstm_kernel<T, 3, DREG>;
+  if (DREG > 0 && SPLIT * dv > threads) return PE_ERR_UNSUPPORTED_SIZE;
+  auto k0 = mlstm_kernel<T, 0, DREG, SPLIT>;
+  auto k1 = mlstm_kernel<T, 1, DREG, SPLIT>;
+  auto k3 = mlstm_kernel<T, 3, DREG, SPLIT>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -244,12 +302,12 @@ static int mlstm_run(const MlstmArgs& a, int max_q, cudaStream_t stream) {
   }
   if (a.chunk > 0) {
     const dim3 grid(a.heads, a.n_seqs, a.max_chunks);
-    launch(k1, grid, dim3(threads), smem, stream, a);
+    launch(k1, grid, dim3(threads), smem, stream, a, batch);
     const int elems = d * dv + d;
     launch(mlstm_chain_kernel, dim3(a.heads, a.n_seqs, (elems + 255) / 256), dim3(256), 0, stream, a);
-    launch(k3, grid, dim3(threads), smem, stream, a);
+    launch(k3, grid, dim3(threads), smem, stream, a, batch);
   } else {
-    launch(k0, dim3(a.heads, a.n_seqs, 1), dim3(threads), smem, stream, a);
+    launch(k0, dim3(a.heads, a.n_seqs, 1), dim3(threads), smem, stream, a, batch);
   }
   (void)max_q;
   return PE_OK;
@@ -281,13 +339,14 @@ extern "C" int pe_mlstm_recurrence(int dtype, const void* q, const void* k, cons
   }
   // the state's columns in registers where a column fits (key sizes up to 128, value sizes up to the block), in shared
   // memory otherwise
-  const int reg = (d <= 32) ? 32 : (d <= 64 && dv <= 512 ? 64 : (d <= 128 && dv <= 256 ? 128 : 0));
-  if (reg == 0 && ((size_t)d * dv + 3 * (size_t)d) * sizeof(float) > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;
+  // 128: two threads a column with 64 rows each (the value size then fills whole half-warps)
+  const int reg = (d <= 32) ? 32 : (d <= 64 && dv <= 512 ? 64 : (d <= 128 && dv <= 256 && dv % 16 == 0 ? 128 : 0));
+  if (reg == 0 && ((size_t)d * dv + 3 * (size_t)d) * sizeof(float) + 2 * (size_t)dv * 4 > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;
   int rc;
 #define PE_MLSTM(T)                                                          \
-  (reg == 32 ? pe::mlstm_run<T, 32>(a, max_q, stream)                        \
-   : reg == 64 ? pe::mlstm_run<T, 64>(a, max_q, stream)                      \
-   : reg == 128 ? pe::mlstm_run<T, 128>(a, max_q, stream) : pe::mlstm_run<T, 0>(a, max_q, stream))
+  (reg == 32 ? pe::mlstm_run<T, 32, 1>(a, max_q, stream)                     \
+   : reg == 64 ? pe::mlstm_run<T, 64, 1>(a, max_q, stream)                   \
+   : reg == 128 ? pe::mlstm_run<T, 64, 2>(a, max_q, stream) : pe::mlstm_run<T, 0, 1>(a, max_q, stream))
   rc = dtype == PE_F32 ? PE_MLSTM(float) : PE_MLSTM(__nv_bfloat16);
 #undef PE_MLSTM
   if (rc != PE_OK) return rc;

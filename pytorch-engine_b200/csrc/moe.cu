@@ -18,7 +18,7 @@ namespace pe {
 
 // One warp per token.
 __global__ void moe_route_kernel(const float* logits, const float* __restrict__ correction, int n_tokens, int n_all, int top,
-                                 int* __restrict__ chosen, float* __restrict__ weight) {
+                                 int* __restrict__ chosen, float* __restrict__ weight, int* __restrict__ dense_rows, int n_real) {
   pdl_wait_block();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
@@ -53,6 +53,8 @@ __global__ void moe_route_kernel(const float* logits, const float* __restrict__ 
       const bool any = best_e != 0x7fffffff;
       chosen[(size_t)t * top + j] = any ? best_e : -1;
       weight[(size_t)t * top + j] = any ? expf(z[best_e] - mx) * inv : 0.f;
+      // where every expert runs on every token, the pair's row is known here
+      if (dense_rows) dense_rows[(size_t)t * top + j] = (any && best_e < n_real) ? t * n_real + best_e : -1;
     }
   }
 }
@@ -280,13 +282,13 @@ __global__ void glu_act_kernel(const T* gate_up, T* __restrict__ out, int n_rows
 }  // namespace pe
 
 extern "C" int pe_moe_route(const float* logits, const float* correction, int n_tokens, int n_all, int top, int* chosen,
-                            float* weight, cudaStream_t stream) {
+                            float* weight, int* dense_rows, int n_real, cudaStream_t stream) {
   if (n_tokens <= 0) return PE_OK;
   if (n_all <= 0 || top <= 0 || top > n_all) return PE_ERR_BAD_ARGUMENT;
   if (n_all > 2048) return PE_ERR_UNSUPPORTED_SIZE;
   const int warps = 4;
   pe::launch(pe::moe_route_kernel, (n_tokens + warps - 1) / warps, warps * 32, 0, stream, logits, correction, n_tokens, n_all,
-             top, chosen, weight);
+             top, chosen, weight, dense_rows, n_real);
   PE_LAUNCH_CHECK();
   return PE_OK;
 }

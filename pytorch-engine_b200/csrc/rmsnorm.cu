@@ -213,10 +213,9 @@ __global__ void rmsnorm_sum_kernel(float* __restrict__ residual, DeltaList delta
   float* res_row = residual + src * dim;
   float ss = 0.f;
   for (int c = threadIdx.x; c < dim; c += blockDim.x) {
-    float add = 0.f;
+    float h = res_row[c];
     for (int i = 0; i < deltas.count; ++i)
-      add = fmaf(deltas.scale[i], to_f32<TDelta>(((const TDelta*)deltas.ptr[i])[src * dim + c]), add);
-    const float h = res_row[c] + add;
+      h = fmaf(deltas.scale[i], to_f32<TDelta>(((const TDelta*)deltas.ptr[i])[src * dim + c]), h);
     row_buf[c] = h;
     ss += h * h;
   }
@@ -226,6 +225,48 @@ __global__ void rmsnorm_sum_kernel(float* __restrict__ residual, DeltaList delta
     const float h = row_buf[c];
     if (write_back) res_row[c] = h;
     if (out) out[(size_t)r * dim + c] = from_f32<TOut>(h * inv * weight[c]);
+  }
+}
+
+// The same with 4-element accesses, for widths that are a multiple of 4 and rows on 16-byte boundaries.
+template <typename TDelta, typename TOut>
+__global__ void __launch_bounds__(1024) rmsnorm_sum_vec4_kernel(float* __restrict__ residual, DeltaList deltas,
+                                                                 const float* __restrict__ weight, TOut* __restrict__ out,
+                                                                 const int* rows, int n_rows, int dim, float eps) {
+  extern __shared__ float row_buf[];  // dim floats
+  __shared__ float red[32];
+  const int c0 = threadIdx.x * 4;
+  float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c0 < dim) w0 = Vec4<float>::load(weight + c0);       // the weight does not come from the kernel before this one
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  if (r >= n_rows) return;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  float* res_row = residual + src * dim;
+  const bool write_back = rows == nullptr;
+  float ss = 0.f;
+  for (int c = c0; c < dim; c += blockDim.x * 4) {
+    float4 h = Vec4<float>::load(res_row + c);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (i < deltas.count) {
+        const float4 d = Vec4<TDelta>::load((const TDelta*)deltas.ptr[i] + src * dim + c);
+        const float sc = deltas.scale[i];
+        h.x = fmaf(sc, d.x, h.x); h.y = fmaf(sc, d.y, h.y); h.z = fmaf(sc, d.z, h.z); h.w = fmaf(sc, d.w, h.w);
+      }
+    }
+    if (write_back) Vec4<float>::store(res_row + c, h);
+    *reinterpret_cast<float4*>(row_buf + c) = h;
+    ss += h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
+  }
+  if (!out) return;
+  const float inv = rsqrtf(block_sum(ss, red) / (float)dim + eps);
+  TOut* o_row = out + (size_t)r * dim;
+  for (int c = c0; c < dim; c += blockDim.x * 4) {
+    const float4 h = *reinterpret_cast<const float4*>(row_buf + c);
+    const float4 w = c == c0 ? w0 : Vec4<float>::load(weight + c);
+    Vec4<TOut>::store(o_row + c, make_float4(h.x * inv * w.x, h.y * inv * w.y, h.z * inv * w.z, h.w * inv * w.w));
   }
 }
 
@@ -331,14 +372,17 @@ extern "C" int pe_rmsnorm_residual_sum(int dtype, float* residual, const void* c
     list.ptr[i] = i < n_deltas ? deltas[i] : nullptr;
     list.scale[i] = i < n_deltas ? scales[i] : 0.f;
   }
-  const int threads = dim >= 4096 ? 1024 : (dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128));
+  int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+  bool vec = (dim % 4 == 0) && ((uintptr_t)residual % 16 == 0) && ((uintptr_t)weight % 16 == 0) && ((uintptr_t)out % 16 == 0);
+  for (int i = 0; i < n_deltas; ++i) vec = vec && ((uintptr_t)deltas[i] % 16 == 0);
+  if (vec && n_rows <= 64 && dim > 2048) threads = 1024;   // a handful of rows: latency counts (see pe_rmsnorm_residual)
   int e;
   if (dtype == PE_F32) {
-    auto k = pe::rmsnorm_sum_kernel<float, float>;
+    auto k = vec ? pe::rmsnorm_sum_vec4_kernel<float, float> : pe::rmsnorm_sum_kernel<float, float>;
     if ((e = pe::set_smem(k, smem))) return e;
     pe::launch(k, n_rows, threads, smem, stream, residual, list, weight, (float*)out, rows, n_rows, dim, eps);
   } else if (dtype == PE_BF16) {
-    auto k = pe::rmsnorm_sum_kernel<__nv_bfloat16, __nv_bfloat16>;
+    auto k = vec ? pe::rmsnorm_sum_vec4_kernel<__nv_bfloat16, __nv_bfloat16> : pe::rmsnorm_sum_kernel<__nv_bfloat16, __nv_bfloat16>;
     if ((e = pe::set_smem(k, smem))) return e;
     pe::launch(k, n_rows, threads, smem, stream, residual, list, weight, (__nv_bfloat16*)out, rows, n_rows, dim, eps);
   } else {

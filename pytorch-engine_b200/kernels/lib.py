@@ -79,7 +79,7 @@ _SIGNATURES = {
     "pe_mlstm_recurrence": [I, P, P, P, P, L, P, P, P, F, F, F, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, P],
     "pe_short_conv_silu": [I, P, L, I, P, I, P, P, P, P, P, I, I, I, I, P, P],
     "pe_delta_rule_recurrence": [I, P, P, P, P, P, P, L, P, F, F, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, P],
-    "pe_moe_route": [P, P, I, I, I, P, P, P],
+    "pe_moe_route": [P, P, I, I, I, P, P, P, I, P],
     "pe_moe_group": [P, I, I, I, P, P, P, P],
     "pe_moe_rows_gemm": [I, I, P, L, P, P, I, I, P, L, P, L, I, I, I, F, F, P],
     "pe_moe_gather_rows": [I, P, P, P, I, P, I, I, P],

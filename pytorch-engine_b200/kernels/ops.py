@@ -334,11 +334,13 @@ def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, pair_o
 
 
 def gemm_smallm_grouped_supported(xs: torch.Tensor, weight: torch.Tensor, group_rows: int) -> bool:
-    """Whether csrc/gemm_smallm.cu takes ``xs [G, M, K]`` times ``weight [G * group_rows, K]`` in one launch."""
-    return (xs.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and xs.dim() == 3 and xs.is_contiguous()
+    """Whether csrc/gemm_smallm.cu takes ``xs [G, M, K]`` (any strides of G and M that keep rows on 16-byte boundaries)
+    times ``weight [G * group_rows, K]`` in one launch."""
+    return (xs.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and xs.dim() == 3 and xs.stride(2) == 1
+            and xs.stride(0) % 8 == 0 and xs.stride(1) % 8 == 0
             and weight.is_contiguous() and xs.shape[1] <= 16 and xs.shape[2] % 8 == 0 and group_rows % 16 == 0
             and weight.shape[0] == xs.shape[0] * group_rows and weight.shape[1] == xs.shape[2]
-            and xs.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and (xs.shape[1] * xs.shape[2]) % 8 == 0)
+            and xs.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
 def gemm_smallm_grouped(xs: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, group_rows: int) -> None:
@@ -348,8 +350,8 @@ def gemm_smallm_grouped(xs: torch.Tensor, weight: torch.Tensor, out: torch.Tenso
     g, m, k = xs.shape
     _need(out.shape[0] == m and out.shape[1] == g * group_rows and out.stride(-1) == 1
           and out.dtype in (torch.bfloat16, torch.float32), "gemm_smallm_grouped: out [M, G * group_rows]")
-    check(library().pe_gemm_smallm_grouped(_ptr(xs), k, m * k, g, group_rows, _ptr(weight), _ptr(out), out.stride(0), m, k,
-                                           1 if out.dtype == torch.float32 else 0, sm_count(xs.device), _stream()),
+    check(library().pe_gemm_smallm_grouped(_ptr(xs), xs.stride(1), xs.stride(0), g, group_rows, _ptr(weight), _ptr(out), out.stride(0),
+                                           m, k, 1 if out.dtype == torch.float32 else 0, sm_count(xs.device), _stream()),
           "gemm_smallm_grouped")
     _count(1)
 
@@ -658,11 +660,16 @@ def delta_rule_scratch_floats(n_seqs: int, heads: int, d: int, dv: int, max_chun
 GLU_KINDS = {"silu": 1, "relu": 2, "clamped_swish": 3}
 
 
-def moe_route(logits: torch.Tensor, correction: torch.Tensor, top: int, chosen: torch.Tensor, weight: torch.Tensor) -> None:
+def moe_route(logits: torch.Tensor, correction: torch.Tensor, top: int, chosen: torch.Tensor, weight: torch.Tensor,
+              dense_rows: Optional[torch.Tensor] = None, n_real: int = 0) -> None:
+    """The router's choice (csrc/moe.cu).  ``dense_rows [N, top]`` int32, if given, gets ``token * n_real + expert`` for a
+    chosen real expert and -1 for an identity expert: the row of the pair where every expert ran on every token."""
     _need(logits.dtype == torch.float32 and logits.is_contiguous() and correction.dtype == torch.float32, "moe_route: float32 logits")
     n, n_all = logits.shape
     _need(chosen.dtype == torch.int32 and weight.dtype == torch.float32 and chosen.numel() == n * top == weight.numel(), "moe_route: outputs")
-    check(library().pe_moe_route(_ptr(logits), _ptr(correction), n, n_all, int(top), _ptr(chosen), _ptr(weight), _stream()), "moe_route")
+    _need(dense_rows is None or (dense_rows.dtype == torch.int32 and dense_rows.numel() == n * top), "moe_route: dense_rows")
+    check(library().pe_moe_route(_ptr(logits), _ptr(correction), n, n_all, int(top), _ptr(chosen), _ptr(weight), _ptr(dense_rows),
+                                 int(n_real), _stream()), "moe_route")
     _count(1)
 
 

@@ -81,6 +81,34 @@ class RoutedExperts:
             self.shared = SwiGLU(sp, {"gate_proj": weights["shared.gate"], "up_proj": weights["shared.up"],
                                       "down_proj": weights["shared.down"]}, runtime)
 
+    def runs_every_expert(self, x: torch.Tensor, n: int) -> bool:
+        """A handful of rows (a decode step): what a step costs is the weights it streams, and the weight-streaming
+        product reads a matrix at six times the rate of the row-group kernel; so unless the pairs are far fewer than the
+        experts, every expert runs on every row (all experts' gate|up rows as one stacked matrix, the down products as
+        one grouped launch), and the sum takes the chosen ones."""
+        rt = self.runtime
+        if not (self.n_experts and rt.dtype == torch.bfloat16 and rt.gemm_backend is None and rt.own_small_gemm
+                and n <= rt.small_gemm_rows and 6 * n * self.top >= self.n_experts):
+            return False
+        return (self.hidden % 16 == 0 and self.intermediate % 8 == 0
+                and ops.gemm_smallm_supported(x, self.gate_up.view(-1, self.hidden)))
+
+    def forward_every_expert(self, x, ctx, logits, chosen, weight) -> torch.Tensor:
+        rt = self.runtime
+        n, E, ff = x.shape[0], self.n_experts, self.intermediate
+        pair_row = ctx.buffer("moe.pair_row", (n, self.top), torch.int32)
+        ops.moe_route(logits, self.correction, self.top, chosen, weight, pair_row, E)
+        gu = ctx.buffer("moe.every_gu", (n, E * 2 * ff), rt.dtype)
+        ops.gemm_smallm(x, self.gate_up.view(E * 2 * ff, self.hidden), gu)
+        act = ctx.buffer("moe.every_act", (n * E, ff), rt.dtype)
+        ops.glu_act(gu.view(n * E, 2 * ff), act, self.activation, self.limit, self.alpha)
+        rows = ctx.buffer("moe.every_rows", (n, E * self.hidden), rt.dtype)
+        ops.gemm_smallm_grouped(act.view(n, E, ff).transpose(0, 1), self.down.view(E * self.hidden, ff), rows, self.hidden)
+        shared = self.shared.forward(x, ctx) if self.shared is not None else None
+        delta = ctx.buffer("moe.delta", (n, self.hidden), rt.dtype)
+        ops.moe_combine(rows.view(n * E, self.hidden), x, shared, pair_row, weight, self.top, delta)
+        return delta
+
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         rt = self.runtime
         n, top = x.shape[0], self.top
@@ -91,6 +119,8 @@ class RoutedExperts:
             logits.copy_(y)
         chosen = ctx.buffer("moe.chosen", (n, top), torch.int32)
         weight = ctx.buffer("moe.weight", (n, top), torch.float32)
+        if self.runs_every_expert(x, n):
+            return self.forward_every_expert(x, ctx, logits, chosen, weight)
         ops.moe_route(logits, self.correction, top, chosen, weight)
         offsets = ctx.buffer("moe.offsets", (self.n_experts + 1,), torch.int32)
         row_token = ctx.buffer("moe.row_token", (n * top,), torch.int32)
