@@ -283,6 +283,7 @@ def lunadra_kernel_pairs(pe, torch, s, hbm_gbs, prompt, batch, context):
         token_seq = torch.arange(n_seqs, dtype=torch.int32, device=dev).repeat_interleave(q_len).contiguous()
         token_pos = torch.arange(q_len, dtype=torch.int32, device=dev).repeat(n_seqs).contiguous() + (0 if q_len > 1 else 5)
         chunked = q_len > 128
+        dchunk = 128 if chunked else 0
         max_chunks = -(-q_len // 64) if chunked else 1
         # the like kernel: the wkv recurrence at its own shape (state heads x 64 x 64)
         WH, wd = s["wkv_heads"], s["wkv_dim"]
@@ -322,9 +323,10 @@ def lunadra_kernel_pairs(pe, torch, s, hbm_gbs, prompt, batch, context):
         gate = torch.randn(n, DH * ddv, device=dev).to(bf)
         o2 = torch.empty(n, DH * ddv, dtype=bf, device=dev)
         S2 = torch.zeros(n_seqs, DH, dd, ddv, device=dev)
-        scratch_d = torch.empty(ops.delta_rule_scratch_floats(n_seqs, DH, dd, ddv, max_chunks), device=dev) if chunked else None
+        dmax = -(-q_len // 128) if chunked else 1
+        scratch_d = torch.empty(ops.delta_rule_scratch_floats(n_seqs, DH, dd, ddv, dmax), device=dev) if chunked else None
         us = us_of(lambda: ops.delta_rule_recurrence(qkv, a_lin, dtb, alog, beta, gate, nw2, 1e-6, dd ** -0.5, o2, S2, slots, qstart, n_seqs,
-                                                     q_len, DH, DG, dd, ddv, status, 64 if chunked else 0, max_chunks, scratch_d))
+                                                     q_len, DH, DG, dd, ddv, status, dchunk, dmax, scratch_d))
         entry(f"{what}: gated delta recurrence, head norm, gate", us,
               roof_us(n * (ch * 2 + DH * dd * 4 + DH * ddv * 4) + n_seqs * DH * dd * ddv * 8, n * DH * dd * ddv * 7.0),
               "wkv_recurrence", us_wkv, roof_wkv)

@@ -300,18 +300,19 @@ __global__ void __launch_bounds__(DREG == 0 ? 1024 : 512) delta_rule_kernel(Delt
       if (DREG > 0 && SPLIT == 2) {
         // whole warps walk together (the two halves of a column meet in a shuffle); a column beyond the matrix
         // carries zeros and is never stored
-        float acc = 0.f;
+        float acc = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
         const float vj = (transition || j >= dv) ? 0.f : to_f32<T>(vb[(size_t)tt * dv + j]);
 #pragma unroll
         for (int i = 0; i < DP; i += 4) {
           const float4 g4 = *reinterpret_cast<const float4*>(gs + i0 + i);
           const float4 k4 = *reinterpret_cast<const float4*>(ks + i0 + i);
           Sr[i] *= g4.x; Sr[i + 1] *= g4.y; Sr[i + 2] *= g4.z; Sr[i + 3] *= g4.w;
-          acc = fmaf(Sr[i], k4.x, acc);
-          acc = fmaf(Sr[i + 1], k4.y, acc);
-          acc = fmaf(Sr[i + 2], k4.z, acc);
-          acc = fmaf(Sr[i + 3], k4.w, acc);
+          acc = fmaf(Sr[i], k4.x, acc);            // four sums side by side: a chain of dependent adds is what
+          acc1 = fmaf(Sr[i + 1], k4.y, acc1);      // the walk would otherwise wait for
+          acc2 = fmaf(Sr[i + 2], k4.z, acc2);
+          acc3 = fmaf(Sr[i + 3], k4.w, acc3);
         }
+        acc = (acc + acc1) + (acc2 + acc3);
         acc += __shfl_xor_sync(0xffffffffu, acc, 16);
         const float uk = beta * (vj - acc * kn) * kn;
 #pragma unroll
@@ -324,14 +325,15 @@ __global__ void __launch_bounds__(DREG == 0 ? 1024 : 512) delta_rule_kernel(Delt
           if (MODE != 1) {
             const float4 q4 = *reinterpret_cast<const float4*>(qs + i0 + i);
             o = fmaf(Sr[i], q4.x, o);
-            o = fmaf(Sr[i + 1], q4.y, o);
-            o = fmaf(Sr[i + 2], q4.z, o);
-            o = fmaf(Sr[i + 3], q4.w, o);
+            o1 = fmaf(Sr[i + 1], q4.y, o1);
+            o2 = fmaf(Sr[i + 2], q4.z, o2);
+            o3 = fmaf(Sr[i + 3], q4.w, o3);
           }
         }
+        o = (o + o1) + (o2 + o3);
         if (MODE != 1) o = (o + __shfl_xor_sync(0xffffffffu, o, 16)) * qn;
       } else if (j < cols) {
-        float acc = 0.f;
+        float acc = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
         const float vj = transition ? 0.f : to_f32<T>(vb[(size_t)tt * dv + j]);
         if (DREG > 0) {
 #pragma unroll
@@ -340,10 +342,11 @@ __global__ void __launch_bounds__(DREG == 0 ? 1024 : 512) delta_rule_kernel(Delt
             const float4 k4 = *reinterpret_cast<const float4*>(ks + i);
             Sr[i] *= g4.x; Sr[i + 1] *= g4.y; Sr[i + 2] *= g4.z; Sr[i + 3] *= g4.w;
             acc = fmaf(Sr[i], k4.x, acc);
-            acc = fmaf(Sr[i + 1], k4.y, acc);
-            acc = fmaf(Sr[i + 2], k4.z, acc);
-            acc = fmaf(Sr[i + 3], k4.w, acc);
+            acc1 = fmaf(Sr[i + 1], k4.y, acc1);
+            acc2 = fmaf(Sr[i + 2], k4.z, acc2);
+            acc3 = fmaf(Sr[i + 3], k4.w, acc3);
           }
+          acc = (acc + acc1) + (acc2 + acc3);
           const float uk = beta * (vj - acc * kn) * kn;
 #pragma unroll
           for (int i = 0; i < DP; i += 4) {
@@ -355,11 +358,12 @@ __global__ void __launch_bounds__(DREG == 0 ? 1024 : 512) delta_rule_kernel(Delt
             if (MODE != 1) {
               const float4 q4 = *reinterpret_cast<const float4*>(qs + i);
               o = fmaf(Sr[i], q4.x, o);
-              o = fmaf(Sr[i + 1], q4.y, o);
-              o = fmaf(Sr[i + 2], q4.z, o);
-              o = fmaf(Sr[i + 3], q4.w, o);
+              o1 = fmaf(Sr[i + 1], q4.y, o1);
+              o2 = fmaf(Sr[i + 2], q4.z, o2);
+              o3 = fmaf(Sr[i + 3], q4.w, o3);
             }
           }
+          o = (o + o1) + (o2 + o3);
         } else {
           for (int i = 0; i < d; ++i) {
             const float s = gs[i] * S[(size_t)i * cols + j];
@@ -402,7 +406,12 @@ __global__ void __launch_bounds__(DREG == 0 ? 1024 : 512) delta_rule_kernel(Delt
 // but the sequence's last); on exit its S part holds chunk c's true start state, chunk 0's being the slot's state.
 // A block takes a few columns of one head's state: thread (i, col) keeps element i of its column, the chunk's
 // transition matrix passes through shared memory (rows padded by one float, so that a read across i has no conflicts).
-__global__ void delta_chain_kernel(DeltaArgs a, int col_tile) {
+// The next chunk's matrix is on its way into registers while this chunk's product runs.  (What a chunk costs here is
+// the arrival of its matrix, 4 d^2 bytes for every block: forms with fewer threads a block and four columns a thread,
+// which halve the shared-memory reads of the product, took two to four times as long.)
+constexpr int kChainLoads = 16;                    // floats of the matrix a thread carries ahead (d * d <= 16 * threads)
+
+__global__ void __launch_bounds__(1024) delta_chain_kernel(DeltaArgs a, int col_tile) {
   extern __shared__ float sm[];
   const int d = a.d, dv = a.dv, head = blockIdx.x, b = blockIdx.y;
   float* Ts = sm;                                  // [d][d + 1]
@@ -420,23 +429,56 @@ __global__ void delta_chain_kernel(DeltaArgs a, int col_tile) {
   float* cs = a.scratch + ((size_t)b * a.max_chunks * a.heads + head) * unit;
   const size_t per = (size_t)a.heads * unit;
   float val = live ? a.S[((size_t)slot * a.heads + head) * d * dv + (size_t)i * dv + j] : 0.f;
+  // this thread's share of a matrix: elements threadIdx.x + r * blockDim.x, at row tr + r * tstep of shared memory
+  const int tr = threadIdx.x / d, tc = threadIdx.x % d, tstep = blockDim.x / d;
+  const bool by_rows = blockDim.x % d == 0;        // else the share is addressed element by element
+  const bool ahead = d * d <= kChainLoads * (int)blockDim.x;   // else a chunk's matrix is loaded when its turn comes
+  float tn[kChainLoads];
+  auto fetch = [&](int c) {
+    const float* Tg = cs + (size_t)c * per + (size_t)d * dv;
+#pragma unroll
+    for (int r = 0; r < kChainLoads; ++r) {
+      const int e = threadIdx.x + r * blockDim.x;
+      tn[r] = e < d * d ? Tg[e] : 0.f;
+    }
+  };
+  if (ahead && n_chunks > 1) fetch(0);
   for (int c = 0; c < n_chunks; ++c) {
     float* u = cs + (size_t)c * per;
     const bool has = c + 1 < n_chunks;
     const float loc = (has && live) ? u[(size_t)i * dv + j] : 0.f;
     if (live) u[(size_t)i * dv + j] = val;
     if (!has) break;
-    const float* Tg = u + (size_t)d * dv;
-    for (int e = threadIdx.x; e < d * d; e += blockDim.x) Ts[(size_t)(e / d) * (d + 1) + e % d] = Tg[e];
+    if (ahead) {
+#pragma unroll
+      for (int r = 0; r < kChainLoads; ++r) {
+        const int e = threadIdx.x + r * blockDim.x;
+        if (e < d * d) {
+          if (by_rows) Ts[(size_t)(tr + r * tstep) * (d + 1) + tc] = tn[r];
+          else Ts[(size_t)(e / d) * (d + 1) + e % d] = tn[r];
+        }
+      }
+    } else {
+      const float* Tg = u + (size_t)d * dv;
+      for (int e = threadIdx.x; e < d * d; e += blockDim.x) Ts[(size_t)(e / d) * (d + 1) + e % d] = Tg[e];
+    }
     if (cj < col_tile) cur[(size_t)cj * d + i] = val;
     __syncthreads();
-    float acc = loc;
+    if (ahead && c + 2 < n_chunks) fetch(c + 1);   // in flight during the product below
+    float acc0 = loc, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
     if (live) {
       const float* trow = Ts + (size_t)i * (d + 1);
       const float* col = cur + (size_t)cj * d;
-      for (int k = 0; k < d; ++k) acc = fmaf(trow[k], col[k], acc);
+      int k = 0;
+      for (; k + 4 <= d; k += 4) {
+        acc0 = fmaf(trow[k], col[k], acc0);
+        acc1 = fmaf(trow[k + 1], col[k + 1], acc1);
+        acc2 = fmaf(trow[k + 2], col[k + 2], acc2);
+        acc3 = fmaf(trow[k + 3], col[k + 3], acc3);
+      }
+      for (; k < d; ++k) acc0 = fmaf(trow[k], col[k], acc0);
     }
-    val = acc;
+    val = (acc0 + acc1) + (acc2 + acc3);
     __syncthreads();
   }
 }

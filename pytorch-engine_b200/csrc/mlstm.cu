@@ -177,6 +177,7 @@ __global__ void __launch_bounds__(DREG == 64 ? 512 : 1024) mlstm_kernel(MlstmArg
       if (j < dv) {
         const float tv = take * to_f32<T>(vb[(size_t)tt * dv + j]);
         float acc = 0.f, nq = 0.f;
+        float acc1 = 0.f, acc2 = 0.f, acc3 = 0.f, nq1 = 0.f, nq2 = 0.f, nq3 = 0.f;
         if (DREG > 0) {
 #pragma unroll
           for (int i = 0; i < DP; i += 4) {
@@ -188,16 +189,18 @@ __global__ void __launch_bounds__(DREG == 64 ? 512 : 1024) mlstm_kernel(MlstmArg
             if (MODE != 1) {
               const float4 q4 = *reinterpret_cast<const float4*>(qs + i0 + i);
               const float4 n4 = *reinterpret_cast<const float4*>(nvec + i0 + i);
-              acc = fmaf(Sr[i], q4.x, acc);
-              acc = fmaf(Sr[i + 1], q4.y, acc);
-              acc = fmaf(Sr[i + 2], q4.z, acc);
-              acc = fmaf(Sr[i + 3], q4.w, acc);
+              acc = fmaf(Sr[i], q4.x, acc);          // four sums side by side: a chain of dependent adds is what
+              acc1 = fmaf(Sr[i + 1], q4.y, acc1);    // the walk would otherwise wait for
+              acc2 = fmaf(Sr[i + 2], q4.z, acc2);
+              acc3 = fmaf(Sr[i + 3], q4.w, acc3);
               nq = fmaf(n4.x, q4.x, nq);
-              nq = fmaf(n4.y, q4.y, nq);
-              nq = fmaf(n4.z, q4.z, nq);
-              nq = fmaf(n4.w, q4.w, nq);
+              nq1 = fmaf(n4.y, q4.y, nq1);
+              nq2 = fmaf(n4.z, q4.z, nq2);
+              nq3 = fmaf(n4.w, q4.w, nq3);
             }
           }
+          acc = (acc + acc1) + (acc2 + acc3);
+          nq = (nq + nq1) + (nq2 + nq3);
           if (SPLIT == 2 && MODE != 1) {           // the column's other half
             acc += __shfl_xor_sync(0xffffffffu, acc, 16);
             nq += __shfl_xor_sync(0xffffffffu, nq, 16);
@@ -249,32 +252,59 @@ __global__ void __launch_bounds__(DREG == 64 ? 512 : 1024) mlstm_kernel(MlstmArg
 
 // Chain the chunks: on entry scratch[c] holds chunk c's end state from an empty start (every chunk but the sequence's
 // last); on exit it holds chunk c's true start state, chunk 0's being the slot's state.  One thread per element of
-// (S, n); every thread follows the scalar chain of maxima itself.
+// (S, n).  The chain of maxima is scalar: thread 0 follows it once per tile of chunks and leaves every chunk's two
+// factors in shared memory; the elements then take eight chunks' loads at a time.
+constexpr int kChainTile = 64;
+
 __global__ void mlstm_chain_kernel(MlstmArgs a) {
+  __shared__ float s_keep[kChainTile], s_take[kChainTile];
+  __shared__ float s_m;
   pdl_wait_block();
   pdl_launch_dependents();
   const int head = blockIdx.x, b = blockIdx.y, d = a.d, dv = a.dv;
   const int e = blockIdx.z * blockDim.x + threadIdx.x;
   const int elems = d * dv + d;
   const int slot = a.seq_slot[b];
-  if (slot < 0 || slot >= a.n_slots || e >= elems) return;
+  if (slot < 0 || slot >= a.n_slots) return;
+  const bool live = e < elems;
   const int q_len = a.seq_qstart[b + 1] - a.seq_qstart[b];
   const int n_chunks = (q_len + a.chunk - 1) / a.chunk;
   const size_t unit = mlstm_unit(d, dv);
   float* cs = a.scratch + ((size_t)b * a.max_chunks * a.heads + head) * unit;   // chunk c: cs + c * per
   const size_t per = (size_t)a.heads * unit;
-  float cur = e < d * dv ? a.S[((size_t)slot * a.heads + head) * d * dv + e] : a.n[((size_t)slot * a.heads + head) * d + (e - d * dv)];
-  float m = a.m[(size_t)slot * a.heads + head];
-  for (int c = 0; c < n_chunks; ++c) {
-    float* u = cs + (size_t)c * per;
-    const bool has = c + 1 < n_chunks;
-    const float loc = has ? u[e] : 0.f, M = has ? u[unit - 3] : 0.f, F = has ? u[unit - 2] : 0.f;
-    u[e] = cur;
-    if (e == 0) u[unit - 1] = m;
-    if (has) {
-      const float m_new = fmaxf(F + m, M);
-      cur = expf(F + m - m_new) * cur + expf(M - m_new) * loc;
-      m = m_new;
+  float cur = 0.f;
+  if (live) cur = e < d * dv ? a.S[((size_t)slot * a.heads + head) * d * dv + e] : a.n[((size_t)slot * a.heads + head) * d + (e - d * dv)];
+  if (threadIdx.x == 0) s_m = a.m[(size_t)slot * a.heads + head];
+  for (int c0 = 0; c0 < n_chunks; c0 += kChainTile) {
+    const int nc = min(kChainTile, n_chunks - c0);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float m = s_m;
+      for (int i = 0; i < nc; ++i) {
+        float* u = cs + (size_t)(c0 + i) * per;
+        const bool has = c0 + i + 1 < n_chunks;
+        const float M = has ? u[unit - 3] : 0.f, F = has ? u[unit - 2] : 0.f;
+        if (e == 0) u[unit - 1] = m;               // the maximum at this chunk's start (block z = 0 writes it)
+        const float m_new = has ? fmaxf(F + m, M) : m;
+        s_keep[i] = has ? expf(F + m - m_new) : 1.f;
+        s_take[i] = has ? expf(M - m_new) : 0.f;
+        m = m_new;
+      }
+      s_m = m;
+    }
+    __syncthreads();
+    if (!live) continue;
+    for (int i0 = 0; i0 < nc; i0 += 8) {
+      float loc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) loc[i] = (i0 + i < nc && c0 + i0 + i + 1 < n_chunks) ? cs[(size_t)(c0 + i0 + i) * per + e] : 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (i0 + i < nc) {
+          cs[(size_t)(c0 + i0 + i) * per + e] = cur;
+          cur = s_keep[i0 + i] * cur + s_take[i0 + i] * loc[i];
+        }
+      }
     }
   }
 }

@@ -26,9 +26,10 @@ from .registry import register
 from .spec import CacheRequest, WeightDecl
 
 
-# tokens per chunk when a prompt is cut into chunks that run side by side; steps whose longest sequence has no more
-# tokens than two chunks walk each sequence in one go
-CHUNK_TOKENS = 64
+# tokens per chunk when a prompt is cut into chunks that run side by side (the chain from chunk to chunk costs a product
+# with a d x d matrix per chunk, so the chunks are longer than the mlstm's); steps whose longest sequence has no more
+# tokens than one chunk walk each sequence in one go
+CHUNK_TOKENS = 128
 
 
 @register("mixer", "gated_delta")
@@ -121,7 +122,7 @@ class GatedDeltaMixer:
         rt.linear(low_g, self.g2, out=gate)
         out = ctx.buffer("delta.out", (n, self.n_heads * self.v_dim), rt.dtype)
         chunk, max_chunks, scratch = 0, 1, None
-        if ctx.max_q > 2 * CHUNK_TOKENS:
+        if ctx.max_q > CHUNK_TOKENS:
             chunk = CHUNK_TOKENS
             max_chunks = -(-ctx.max_q // chunk)
             scratch = ctx.buffer("delta.scratch", (ops.delta_rule_scratch_floats(ctx.n_seqs, self.n_heads, self.head_dim, self.v_dim,
