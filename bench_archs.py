@@ -376,13 +376,24 @@ def lunadra_kernel_pairs(pe, torch, s, hbm_gbs, prompt, batch, context):
         act = torch.empty(n * top, ff, dtype=bf, device=dev)
         route()
         if what == "decode":
-            us = us_of(lambda: ops.moe_rows_gemm(x, row_token, offsets, E, n * top, gate_up, act, 3, 7.0, 1.702))
-            dense = (torch.randn(E * 2 * ff, width, device=dev) * 0.02).to(bf)
+            # what a decode step runs: every expert on every row through the weight-streaming product, then the activation
+            stacked = gate_up.view(E * 2 * ff, width)
+            gu = torch.empty(n, E * 2 * ff, dtype=bf, device=dev)
+            act_all = torch.empty(n * E, ff, dtype=bf, device=dev)
+
+            def every_expert():
+                ops.gemm_smallm(x, stacked, gu)
+                ops.glu_act(gu.view(n * E, 2 * ff), act_all, "clamped_swish", 7.0, 1.702)
+            us = us_of(every_expert)
             act2 = torch.empty(n, E * ff, dtype=bf, device=dev)
-            us_like = us_of(lambda: ops.gemm_smallm(x, dense, act2, pair_offset=E * ff))
+            us_like = us_of(lambda: ops.gemm_smallm(x, stacked, act2, pair_offset=E * ff))
             nbytes = E * 2 * ff * width * 2
-            entry("decode: experts' gate|up product with activation (every expert's weights once)", us, roof_us(nbytes),
-                  "gemm_smallm with SiLU epilogue, same bytes", us_like, roof_us(nbytes))
+            entry("decode: experts' gate|up product, then the activation (2 kernels; every expert's weights once)", us, roof_us(nbytes),
+                  "gemm_smallm with SiLU epilogue, same matrix", us_like, roof_us(nbytes))
+            # the row-group kernel, which runs instead where the pairs are far fewer than the experts and in float32
+            us = us_of(lambda: ops.moe_rows_gemm(x, row_token, offsets, E, n * top, gate_up, act, 3, 7.0, 1.702))
+            entry("decode: the same through the row-group kernel (not what a step of this size runs)", us, roof_us(nbytes),
+                  "gemm_smallm with SiLU epilogue, same matrix", us_like, roof_us(nbytes))
         else:
             xs = torch.empty(n * top, width, dtype=bf, device=dev)
 

@@ -155,6 +155,64 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return r;
 }
 
+
+// ---- staging rows of a batch of tokens in shared memory, 16 bytes a thread where the rows allow ------------------------
+template <typename T> struct StageVec;
+template <> struct StageVec<float> { static constexpr int N = 4; };
+template <> struct StageVec<__nv_bfloat16> { static constexpr int N = 8; };
+
+template <typename T>
+__device__ __forceinline__ bool stage_vec_ok(const T* src, long long src_ld, int width) {
+  return width % StageVec<T>::N == 0 && (src_ld * (long long)sizeof(T)) % 16 == 0 && ((uintptr_t)src % 16) == 0;
+}
+
+// dst[r][0..width) = float(src[r][0..width)) * scale;  dst rows dst_ld floats apart (16-byte aligned when vec)
+template <typename T>
+__device__ __forceinline__ void stage_rows_f32(float* dst, int dst_ld, const T* src, long long src_ld, int n_rows, int width,
+                                               float scale, bool vec) {
+  if (vec) {
+    constexpr int N = StageVec<T>::N;
+    const int per_row = width / N;
+    for (int e = threadIdx.x; e < n_rows * per_row; e += blockDim.x) {
+      const int r = e / per_row, c = (e - r * per_row) * N;
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + (size_t)r * src_ld + c);
+      float* o = dst + (size_t)r * dst_ld + c;
+      if (sizeof(T) == 4) {
+        const float4 f = *reinterpret_cast<const float4*>(&raw);
+        *reinterpret_cast<float4*>(o) = make_float4(f.x * scale, f.y * scale, f.z * scale, f.w * scale);
+      } else {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]), c2 = __bfloat1622float2(h[2]), d2 = __bfloat1622float2(h[3]);
+        *reinterpret_cast<float4*>(o) = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+        *reinterpret_cast<float4*>(o + 4) = make_float4(c2.x * scale, c2.y * scale, d2.x * scale, d2.y * scale);
+      }
+    }
+  } else {
+    for (int e = threadIdx.x; e < n_rows * width; e += blockDim.x) {
+      const int r = e / width, c = e - r * width;
+      dst[(size_t)r * dst_ld + c] = to_f32<T>(src[(size_t)r * src_ld + c]) * scale;
+    }
+  }
+}
+
+// dst[r][0..width) = src[r][0..width), rows of dst packed
+template <typename T>
+__device__ __forceinline__ void stage_rows_raw(T* dst, const T* src, long long src_ld, int n_rows, int width, bool vec) {
+  if (vec) {
+    constexpr int N = StageVec<T>::N;
+    const int per_row = width / N;
+    for (int e = threadIdx.x; e < n_rows * per_row; e += blockDim.x) {
+      const int r = e / per_row, c = (e - r * per_row) * N;
+      *reinterpret_cast<uint4*>(dst + (size_t)r * width + c) = *reinterpret_cast<const uint4*>(src + (size_t)r * src_ld + c);
+    }
+  } else {
+    for (int e = threadIdx.x; e < n_rows * width; e += blockDim.x) {
+      const int r = e / width, c = e - r * width;
+      dst[(size_t)r * width + c] = src[(size_t)r * src_ld + c];
+    }
+  }
+}
+
 }  // namespace pe
 
 // ---- error codes of the extern "C" launchers (negative; CUDA runtime errors are returned positive)

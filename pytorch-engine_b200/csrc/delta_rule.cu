@@ -253,24 +253,28 @@ __global__ void __launch_bounds__(DREG == 0 ? 1024 : 512) delta_rule_kernel(Delt
   const float rate = expf(a.A_log[head]);
   const float nw = (MODE != 1 && j < dv) ? a.norm_w[j] : 0.f;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  // 16-byte staging where the rows allow it (a token's rows keep their alignment from token to token)
+  const bool smem_ok = dpad % 4 == 0 && (DREG > 0 || (d * (dv > d ? dv : d)) % 4 == 0);
+  const bool vec_k = smem_ok && stage_vec_ok<T>(x + (size_t)t0 * channels + k_col + kvh * d, channels, d);
+  const bool vec_q = smem_ok && stage_vec_ok<T>(x + (size_t)t0 * channels + kvh * d, channels, d);
+  const bool vec_v = smem_ok && stage_vec_ok<T>(x + (size_t)t0 * channels + v_col + head * dv, channels, dv);
+  const bool vec_g = smem_ok && stage_vec_ok<T>((const T*)a.gate + (size_t)t0 * a.gate_ld + head * dv, a.gate_ld, dv);
   for (int tb = t0; tb < t1; tb += batch) {
     const int nb = min(batch, t1 - tb);
     __syncthreads();                               // the batch before this one has been read
+    stage_rows_f32<T>(kb, dpad, x + (size_t)tb * channels + k_col + kvh * d, channels, nb, d, 1.f, vec_k);
+    if (MODE != 1) stage_rows_f32<T>(qb, dpad, x + (size_t)tb * channels + kvh * d, channels, nb, d, 1.f, vec_q);
+    // the decays: exp(-exp(A) softplus(a + dt)) per token and key channel
     for (int e = threadIdx.x; e < nb * d; e += blockDim.x) {
       const int tt = e / d, i = e - tt * d;
-      const size_t row = (size_t)(tb + tt) * channels;
-      kb[(size_t)tt * dpad + i] = to_f32<T>(x[row + k_col + kvh * d + i]);
-      if (MODE != 1) qb[(size_t)tt * dpad + i] = to_f32<T>(x[row + kvh * d + i]);
       const float z = a.a[(size_t)(tb + tt) * a.heads * d + head * d + i] + a.dt_bias[head * d + i];
       const float softplus = z > 20.f ? z : log1pf(expf(z));
       db[(size_t)tt * dpad + i] = expf(-rate * softplus);
     }
-    if (!transition)
-      for (int e = threadIdx.x; e < nb * dv; e += blockDim.x) {
-        const int tt = e / dv, jj = e - tt * dv;
-        vb[e] = x[(size_t)(tb + tt) * channels + v_col + head * dv + jj];
-        if (MODE != 1) gb[e] = ((const T*)a.gate)[(size_t)(tb + tt) * a.gate_ld + head * dv + jj];
-      }
+    if (!transition) {
+      stage_rows_raw<T>(vb, x + (size_t)tb * channels + v_col + head * dv, channels, nb, dv, vec_v);
+      if (MODE != 1) stage_rows_raw<T>(gb, (const T*)a.gate + (size_t)tb * a.gate_ld + head * dv, a.gate_ld, nb, dv, vec_g);
+    }
     if (threadIdx.x < nb) s_beta[threadIdx.x] = 1.f / (1.f + expf(-a.b[(size_t)(tb + threadIdx.x) * a.heads + head]));
     __syncthreads();
     for (int tt = warp; tt < nb; tt += n_warps) {  // a warp per token: the lengths of k and q

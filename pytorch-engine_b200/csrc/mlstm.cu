@@ -136,19 +136,19 @@ __global__ void __launch_bounds__(DREG == 64 ? 512 : 1024) mlstm_kernel(MlstmArg
   const float bi = a.gate_bias[head], bf = a.gate_bias[a.heads + head];
   const float nw = (MODE != 1 && j < dv) ? a.norm_w[head * dv + j] : 0.f;
   const T* q = (const T*)a.q; const T* k = (const T*)a.k; const T* v = (const T*)a.v; const T* g = (const T*)a.g;
+  // 16-byte staging where the rows allow it (a token's rows keep their alignment from token to token)
+  const bool smem_ok = dpad % 4 == 0 && (DREG > 0 || (d * dv) % 4 == 0);
+  const bool vec_k = smem_ok && stage_vec_ok<T>(k + (size_t)t0 * a.ld + head * d, a.ld, d);
+  const bool vec_q = smem_ok && stage_vec_ok<T>(q + (size_t)t0 * a.ld + head * d, a.ld, d);
+  const bool vec_v = smem_ok && stage_vec_ok<T>(v + (size_t)t0 * a.ld + head * dv, a.ld, dv);
+  const bool vec_g = smem_ok && stage_vec_ok<T>(g + (size_t)t0 * a.ld + head * dv, a.ld, dv);
   for (int tb = t0; tb < t1; tb += batch) {
     const int nb = min(batch, t1 - tb);
     __syncthreads();                               // the batch before this one has been read
-    for (int e = threadIdx.x; e < nb * d; e += blockDim.x) {
-      const int tt = e / d, i = e - tt * d;
-      kb[(size_t)tt * dpad + i] = to_f32<T>(k[(size_t)(tb + tt) * a.ld + head * d + i]);
-      if (MODE != 1) qb[(size_t)tt * dpad + i] = to_f32<T>(q[(size_t)(tb + tt) * a.ld + head * d + i]) * a.q_scale;
-    }
-    for (int e = threadIdx.x; e < nb * dv; e += blockDim.x) {
-      const int tt = e / dv, jj = e - tt * dv;
-      vb[e] = v[(size_t)(tb + tt) * a.ld + head * dv + jj];
-      if (MODE != 1) gb[e] = g[(size_t)(tb + tt) * a.ld + head * dv + jj];
-    }
+    stage_rows_f32<T>(kb, dpad, k + (size_t)tb * a.ld + head * d, a.ld, nb, d, 1.f, vec_k);
+    if (MODE != 1) stage_rows_f32<T>(qb, dpad, q + (size_t)tb * a.ld + head * d, a.ld, nb, d, a.q_scale, vec_q);
+    stage_rows_raw<T>(vb, v + (size_t)tb * a.ld + head * dv, a.ld, nb, dv, vec_v);
+    if (MODE != 1) stage_rows_raw<T>(gb, g + (size_t)tb * a.ld + head * dv, a.ld, nb, dv, vec_g);
     if (threadIdx.x < nb) {
       const int t = tb + threadIdx.x;
       s_keep[threadIdx.x] = a.cap * tanhf((a.gates[(size_t)t * 2 * a.heads + head] + bi) / a.cap);
