@@ -11,7 +11,7 @@
                          "shared": {"ff", "limit"}}}, ...]}
 
 Every size and constant is read from there; nothing is the same for two layers unless the file says so.  A layer type
-``mlstm_<anything>`` is an ``mlstm`` layer.  The ranks of the gated delta mixer's low-rank projections are not in the
+``mlstm_<anything>`` is an ``mlstm`` layer (and ``parallel_<anything>`` a ``parallel`` one).  The ranks of the gated delta mixer's low-rank projections are not in the
 file: the checkpoint's tensors decide them (``rank`` is what random weights get).
 """
 from __future__ import annotations
@@ -172,7 +172,7 @@ class LunadraConfig(ModelConfig):
             entry = _obj(entry, where)
             kind = entry.get("type")
             m = _obj(entry.get("mixer"), where + ".mixer")
-            if kind == "parallel":
+            if isinstance(kind, str) and (kind == "parallel" or kind.startswith("parallel_")):
                 lw = where + ".mixer.left"
                 left = _obj(m.get("left"), lw)
                 whole, num = _sub(left, lw)

@@ -248,20 +248,65 @@ __global__ void moe_gather_kernel(const T* x, const int* row_token, const int* o
 template <typename T>
 __global__ void moe_combine_kernel(const T* rows, const T* x, const T* shared, const int* pair_row, const float* weight,
                                    int top, T* __restrict__ out, int n_tokens, int width) {
+  constexpr int kKeep = 32;            // a token's rows and weights, read once (more choices than this: the rest from global memory)
+  __shared__ int s_row[kKeep];
+  __shared__ float s_w[kKeep];
   pdl_wait_block();
   pdl_launch_dependents();
   const int t = blockIdx.x;
   if (t >= n_tokens) return;
+  if (threadIdx.x < top && threadIdx.x < kKeep) {
+    s_row[threadIdx.x] = pair_row[(size_t)t * top + threadIdx.x];
+    s_w[threadIdx.x] = weight[(size_t)t * top + threadIdx.x];
+  }
+  __syncthreads();
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j < top; ++j) {
-      const int r = pair_row[(size_t)t * top + j];
-      const float wj = weight[(size_t)t * top + j];
+      const int r = j < kKeep ? s_row[j] : pair_row[(size_t)t * top + j];
+      const float wj = j < kKeep ? s_w[j] : weight[(size_t)t * top + j];
       const float v = r >= 0 ? to_f32<T>(rows[(size_t)r * width + c]) : to_f32<T>(x[(size_t)t * width + c]);
       acc = fmaf(wj, v, acc);
     }
     if (shared) acc += to_f32<T>(shared[(size_t)t * width + c]);
     out[(size_t)t * width + c] = from_f32<T>(acc);
+  }
+}
+
+// The same for bfloat16 rows whose width is a multiple of 8 and that start on 16-byte boundaries: a thread takes eight
+// channels of a token, 16-byte loads and stores (a token's rows and weights are read once per eight channels).
+__global__ void moe_combine_vec8_kernel(const __nv_bfloat16* rows, const __nv_bfloat16* x, const __nv_bfloat16* shared,
+                                        const int* pair_row, const float* weight, int top, __nv_bfloat16* __restrict__ out,
+                                        int n_tokens, int width) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int per_row = width / 8;
+  const size_t total = (size_t)n_tokens * per_row;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / per_row), c = (int)(idx - (size_t)t * per_row) * 8;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    auto add = [&](const __nv_bfloat16* p, float w) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(p);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] = fmaf(w, f.x, acc[2 * e]);
+        acc[2 * e + 1] = fmaf(w, f.y, acc[2 * e + 1]);
+      }
+    };
+    for (int j = 0; j < top; ++j) {
+      const int r = pair_row[(size_t)t * top + j];
+      add(r >= 0 ? rows + (size_t)r * width + c : x + (size_t)t * width + c, weight[(size_t)t * top + j]);
+    }
+    if (shared) add(shared + (size_t)t * width + c, 1.f);
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+    *reinterpret_cast<uint4*>(out + (size_t)t * width + c) = o;
   }
 }
 
@@ -360,7 +405,15 @@ extern "C" int pe_moe_combine(int dtype, const void* rows, const void* x, const 
   if (n_tokens <= 0) return PE_OK;
   if (top <= 0 || width <= 0) return PE_ERR_BAD_ARGUMENT;
   const int threads = width >= 1024 ? 256 : 128;
-  if (dtype == PE_F32)
+  const bool vec8 = dtype == PE_BF16 && width % 8 == 0 && (uintptr_t)rows % 16 == 0 && (uintptr_t)x % 16 == 0 &&
+                    (uintptr_t)shared % 16 == 0 && (uintptr_t)out % 16 == 0;
+  if (vec8) {
+    const size_t total = (size_t)n_tokens * (width / 8);
+    size_t blocks = (total + 127) / 128;
+    if (blocks > (size_t)pe::kSMs * 32) blocks = (size_t)pe::kSMs * 32;
+    pe::launch(pe::moe_combine_vec8_kernel, (int)blocks, 128, 0, stream, (const __nv_bfloat16*)rows, (const __nv_bfloat16*)x,
+               (const __nv_bfloat16*)shared, pair_row, weight, top, (__nv_bfloat16*)out, n_tokens, width);
+  } else if (dtype == PE_F32)
     pe::launch(pe::moe_combine_kernel<float>, n_tokens, threads, 0, stream, (const float*)rows, (const float*)x, (const float*)shared,
                pair_row, weight, top, (float*)out, n_tokens, width);
   else if (dtype == PE_BF16)

@@ -112,10 +112,14 @@ class GatedDeltaMixer:
         qkv = ctx.buffer("delta.qkv", (n, c), rt.dtype)
         tail = view.state("conv") if self.taps > 1 else self.no_tail
         ops.short_conv_silu(wide, 0, self.conv_w, tail, ctx.token_seq, ctx.seq_slot, ctx.seq_qstart, qkv, ctx.n_seqs, rt.status)
-        low_a = ctx.buffer("delta.low_a", (n, ra), rt.dtype)
-        low_a.copy_(wide[:, c:c + ra])
-        low_g = ctx.buffer("delta.low_g", (n, self.rank_g), rt.dtype)
-        low_g.copy_(wide[:, c + ra:])
+        if n < rt.large_gemm_rows and c % 8 == 0 and ra % 8 == 0:
+            # the low ranks as views of the wide product's rows (the products for few and for some rows take strided rows)
+            low_a, low_g = wide[:, c:c + ra], wide[:, c + ra:]
+        else:
+            low_a = ctx.buffer("delta.low_a", (n, ra), rt.dtype)
+            low_a.copy_(wide[:, c:c + ra])
+            low_g = ctx.buffer("delta.low_g", (n, self.rank_g), rt.dtype)
+            low_g.copy_(wide[:, c + ra:])
         decay = self._f32_linear(low_a, self.a2, ctx.buffer("delta.decay", (n, self.n_heads * self.head_dim), torch.float32))
         beta = self._f32_linear(x, self.b_proj, ctx.buffer("delta.beta", (n, self.n_heads), torch.float32))
         gate = ctx.buffer("delta.gate", (n, self.n_heads * self.v_dim), rt.dtype)
