@@ -413,25 +413,28 @@ def test_unequal_batches_on_slots_used_again(pe, models, key, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_a_decode_batch_of_twelve(pe, models, dtype):
-    """More sequences than the weight-streaming products take, inside the captured decode step."""
+@pytest.mark.parametrize("count", [12, 40])
+def test_a_decode_batch_of_many(pe, models, dtype, count):
+    """More sequences than the weight-streaming products take, inside the captured decode step: twelve (the experts'
+    row-group kernel) and forty (80 pairs: in bfloat16 the library's product over row groups, recorded in the graph)."""
     key = "B"
-    eng = models.engine(key, dtype, max_batch=12)
+    eng = models.engine(key, dtype, max_batch=count, max_cache_tokens=64 * (count + 2))
     vocab = CONFIGS[key]["vocab"]
-    seqs = [_tokens(vocab, 3 + i + 6, 300 + i) for i in range(12)]
+    seqs = [_tokens(vocab, 3 + i % 13 + 6, 300 + i) for i in range(count)]
     slots = [eng.alloc_slot() for _ in seqs]
-    got = {i: [] for i in range(12)}
-    out = eng.step([_entry(pe, s, q[:3 + i], [2 + i]) for i, (s, q) in enumerate(zip(slots, seqs))]).clone()
-    for i in range(12):
+    got = {i: [] for i in range(count)}
+    out = eng.step([_entry(pe, s, q[:len(q) - 6], [len(q) - 7]) for s, q in zip(slots, seqs)]).clone()
+    for i in range(count):
         got[i].append(out[i:i + 1])
     for step in range(6):
-        out = eng.step([_entry(pe, s, [q[3 + i + step]], [0]) for i, (s, q) in enumerate(zip(slots, seqs))]).clone()
-        for i in range(12):
+        out = eng.step([_entry(pe, s, [q[len(q) - 6 + step]], [0]) for s, q in zip(slots, seqs)]).clone()
+        for i in range(count):
             got[i].append(out[i:i + 1])
     for s in slots:
         eng.free_slot(s)
-    for i in (0, 5, 11):
-        models.check(key, dtype, seqs[i], torch.cat(got[i]), range(2 + i, 9 + i), f"{key} request {i} of twelve")
+    for i in (0, 5, count - 1):
+        n = len(seqs[i])
+        models.check(key, dtype, seqs[i], torch.cat(got[i]), range(n - 7, n), f"{key} request {i} of {count}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
